@@ -13,9 +13,11 @@ What is different:
 * a sequence is a *slot record* (state, length, blocks); slots come from a
   LIFO free list and go back when a sequence ends, so batch after batch reuses
   slots and blocks;
-* layers are gathered into *groups* with the same needs (all keys, or a window
-  of them; KV heads; head size).  Each group has its own pool, allocator and
-  block table; a window group gives blocks back as they fall behind the window;
+* layers are gathered into *groups* with the same needs (all keys, a window of
+  them, or the keys of the current chunk; KV heads; head sizes of keys and of
+  values).  Each group has its own pool, allocator and block table; a window
+  group gives blocks back as they fall behind the window, a chunk group those
+  that lie wholly before the chunk of the next query;
 * beside the paged storage there is per-sequence state of fixed size, indexed
   by slot, for mixers that carry a recurrent state instead of keys.
 
@@ -46,11 +48,29 @@ DEFAULT_BLOCK_SIZE = 64
 class KVGroupSpec:
     """Layers that share one kind of key/value storage.  ``window`` None: all
     keys are kept; a number: only blocks that still hold one of the last
-    ``window`` positions."""
+    ``window`` positions.  ``chunk``: a query sees only the keys of its own
+    chunk of that many positions (counted from the start of the sequence), so
+    only blocks that reach into the chunk of the next query are kept.
+    ``v_head_dim``: size of a value head where it differs from a key head's."""
     n_layers: int
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    def first_needed(self, length: int) -> int:
+        """The first position that the query at position ``length`` (the next one) can still see."""
+        first = 0
+        if self.window is not None:
+            first = max(first, length - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, (length // self.chunk) * self.chunk)
+        return first
 
 
 @dataclass(frozen=True)
@@ -77,9 +97,17 @@ class KVGroup:
         self.num_blocks = num_blocks
         self.block_size = block_size
         self.max_blocks_per_seq = max_blocks_per_seq
-        # [layer, k|v, block, kv head, token in block, dim]
-        self.pool = torch.zeros((spec.n_layers, 2, num_blocks, spec.n_kv_heads, block_size, spec.head_dim),
-                                dtype=dtype, device=device)
+        # [layer, k|v, block, kv head, token in block, dim]; keys and values of different head sizes: a pool each
+        if spec.value_dim == spec.head_dim:
+            self.pool = torch.zeros((spec.n_layers, 2, num_blocks, spec.n_kv_heads, block_size, spec.head_dim),
+                                    dtype=dtype, device=device)
+            self.keys, self.values = self.pool[:, 0], self.pool[:, 1]
+        else:
+            self.pool = None
+            self.keys = torch.zeros((spec.n_layers, num_blocks, spec.n_kv_heads, block_size, spec.head_dim),
+                                    dtype=dtype, device=device)
+            self.values = torch.zeros((spec.n_layers, num_blocks, spec.n_kv_heads, block_size, spec.value_dim),
+                                      dtype=dtype, device=device)
         self.alloc = IdAllocator(num_blocks, "block")
         self.table_host = np.full((max_slots, max_blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, max_blocks_per_seq), -1, dtype=torch.int32, device=device)
@@ -90,10 +118,10 @@ class KVGroup:
         self._dev_updates: Optional[torch.Tensor] = None
 
     def k_pool(self, layer: int) -> torch.Tensor:
-        return self.pool[layer, 0]
+        return self.keys[layer]
 
     def v_pool(self, layer: int) -> torch.Tensor:
-        return self.pool[layer, 1]
+        return self.values[layer]
 
     def set_entry(self, slot: int, col: int, block: int) -> None:
         self.table_host[slot, col] = block
@@ -134,7 +162,7 @@ class KVGroup:
 
     def bytes_per_token(self) -> int:
         s = self.spec
-        return 2 * s.n_layers * s.n_kv_heads * s.head_dim * self.pool.element_size()
+        return s.n_layers * s.n_kv_heads * (s.head_dim + s.value_dim) * self.keys.element_size()
 
 
 class PagedCache:
@@ -230,20 +258,18 @@ class PagedCache:
                 g.set_entry(slot, c, b)
 
     def advance(self, slot: int, n: int) -> None:
-        """The step's tokens are in the cache: lengthen, and let window groups
-        give back blocks that no later query can see."""
+        """The step's tokens are in the cache: lengthen, and let window and chunk
+        groups give back blocks that no later query can see."""
         rec = self._record(slot)
         if self.blocks_needed(rec.length + n) > min((len(b) for b in rec.blocks), default=1 << 30):
             raise ValueError(f"slot {slot}: advancing by {n} beyond the reserved blocks")
         rec.length += n
         self.lengths_version += 1
         for gi, g in enumerate(self.groups):
-            w = g.spec.window
-            if w is None:
+            if g.spec.window is None and g.spec.chunk is None:
                 continue
-            # the next query sits at position `length` and sees keys > length - w
-            first_needed = max(0, rec.length - w + 1)
-            dead_cols = first_needed // self.block_size
+            # the next query sits at position `length`
+            dead_cols = g.spec.first_needed(rec.length) // self.block_size
             blocks = rec.blocks[gi]
             freed = []
             for c in range(min(dead_cols, len(blocks))):
@@ -271,13 +297,13 @@ class PagedCache:
         rec = self._record(slot)
         g = self.groups[group]
         s = g.spec
-        k = torch.zeros((rec.length, s.n_kv_heads, s.head_dim), dtype=g.pool.dtype, device=g.pool.device)
-        v = torch.zeros_like(k)
+        k = torch.zeros((rec.length, s.n_kv_heads, s.head_dim), dtype=g.keys.dtype, device=g.keys.device)
+        v = torch.zeros((rec.length, s.n_kv_heads, s.value_dim), dtype=g.keys.dtype, device=g.keys.device)
         for pos in range(rec.length):
             b = rec.blocks[group][pos // self.block_size]
             if b >= 0:
-                k[pos] = g.pool[layer, 0, b, :, pos % self.block_size]
-                v[pos] = g.pool[layer, 1, b, :, pos % self.block_size]
+                k[pos] = g.keys[layer, b, :, pos % self.block_size]
+                v[pos] = g.values[layer, b, :, pos % self.block_size]
         return k, v
 
     def kv_bytes(self, slots: Optional[Sequence[int]] = None) -> int:
@@ -289,8 +315,7 @@ class PagedCache:
         for g in self.groups:
             for s in slots:
                 n = self._record(s).length
-                if g.spec.window is not None:
-                    n = min(n, g.spec.window)
+                n -= g.spec.first_needed(max(0, n - 1))      # what the last cached token's query saw
                 total += n * g.bytes_per_token()
         return total
 

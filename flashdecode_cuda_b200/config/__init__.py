@@ -1,7 +1,8 @@
 """Configurations: reading ``config.json`` and the named presets.
 
 ``load_config`` picks the configuration class through the architecture
-registry, from ``config.json["architectures"][0]``.
+registry, from ``config.json["architectures"][0]`` or, where the file names its
+design in one string, ``config.json["architecture"]``.
 """
 
 from __future__ import annotations
@@ -11,6 +12,7 @@ from pathlib import Path
 from typing import Any, Dict, List, Union
 
 from ..registry import architecture
+from .lonasun import LonasunConfig
 from .qwen2 import ConfigError, Qwen2Config
 
 PRESET_DIR = Path(__file__).resolve().parent / "presets"
@@ -30,9 +32,9 @@ def preset_dict(name: str) -> Dict[str, Any]:
 
 
 def config_from_dict(cfg: Dict[str, Any]):
-    archs = cfg.get("architectures")
+    archs = cfg.get("architectures") or ([cfg["architecture"]] if cfg.get("architecture") else None)
     if not archs:
-        raise ConfigError("config.json has no 'architectures' entry to choose the model by")
+        raise ConfigError("config.json has no 'architectures' (or 'architecture') entry to choose the model by")
     try:
         arch = architecture(archs[0])
     except KeyError as e:
@@ -58,4 +60,4 @@ def load_config(source: Union[str, Path, Dict[str, Any]]):
     raise ConfigError(f"no config.json at {source!r} and no preset of that name; presets: {preset_names()}")
 
 
-__all__ = ["ConfigError", "Qwen2Config", "load_config", "config_from_dict", "preset_dict", "preset_names"]
+__all__ = ["ConfigError", "Qwen2Config", "LonasunConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]

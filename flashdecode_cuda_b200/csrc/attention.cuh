@@ -8,11 +8,11 @@ namespace fd {
 struct AttnParams {
     const void* q;             // [T, n_q * d]
     const void* k_pool;        // [num_blocks, n_kv, block_size, d]
-    const void* v_pool;
-    void* out;                 // [T, n_q * d]
+    const void* v_pool;        // [num_blocks, n_kv, block_size, dv]
+    void* out;                 // [T, n_q * dv]
     float* part_m;             // [T, n_q, n_splits]
     float* part_l;
-    float* part_acc;           // [T, n_q, n_splits, d]
+    float* part_acc;           // [T, n_q, n_splits, dv]
     const int* block_table;    // [slots, max_blocks]
     const int* row_slot;       // per batch row: cache slot, or -1 for a padding row
     const int* row_q_start;    // first token of the row in the flat token arrays
@@ -22,7 +22,9 @@ struct AttnParams {
     int* counters;             // [rows, n_kv] arrival counts for the in-kernel merge of the splits (all zero between launches), or null
     int max_blocks, num_blocks, block_size;
     int n_q, n_kv, G, d;
+    int dv;                    // size of a value head (= d in the tensor-core kernels)
     int QT, n_splits, split_len, window;
+    int chunk;                 // > 0: a query at position i sees key j <= i only if i / chunk == j / chunk
     float scale;
     // decode steps on the tensor cores only: memory that a later kernel streams (the next part's first weights), or
     // null; every CTA asks L2 for its share once its own keys and values are through

@@ -65,6 +65,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
     }
     const int ctx = p.row_ctx_len[b];
     int lo = p.window > 0 ? max(0, ctx - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, (ctx / p.chunk) * p.chunk);      // chunked visibility: from the start of the query's chunk
     int hi = ctx + 1;                           // the new token's own key is already in the cache
     if (p.n_splits > 1) {
         lo = max(lo, split * p.split_len);

@@ -40,7 +40,8 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const int kvh = h / p.G;
     const int p_first = ctx + tile * PM_BM;          // position of this CTA's first query
     const int hi = p_first + nq;                      // keys 0 .. last query position
-    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int chunk = p.chunk;        // > 0: a query sees the keys of its own chunk of this many positions only
+    const int lo = max(p.window > 0 ? max(0, p_first - p.window + 1) : 0, chunk > 0 ? (p_first / chunk) * chunk : 0);
 
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                        // [64][D]
@@ -107,6 +108,9 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const int row_a = warp * 16 + (lane >> 2);        // this thread's rows: row_a and row_a + 8
     const int pos_a = p_first + row_a, pos_b = pos_a + 8;
     const int w_first = p_first + warp * 16, w_last = w_first + 15;     // positions of the warp's rows
+    // first visible key of this thread's rows and of the warp's first and last row under chunked visibility
+    const int cs_a = chunk > 0 ? (pos_a / chunk) * chunk : 0, cs_b = chunk > 0 ? (pos_b / chunk) * chunk : 0;
+    const int cs_first = chunk > 0 ? (w_first / chunk) * chunk : 0, cs_last = chunk > 0 ? (w_last / chunk) * chunk : 0;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int t0 = t_begin + it * PM_BN;
@@ -126,7 +130,8 @@ attn_prefill_mma_kernel(const AttnParams p) {
         const unsigned char* ks_ = k_s + (it & 1) * TILE_BYTES;
         const unsigned char* vs_ = v_s + (it & 1) * TILE_BYTES;
         // a tile wholly in the future of all rows of this warp contributes nothing
-        const bool skip = t0 > w_last || (p.window > 0 && t0 + PM_BN - 1 < w_first - p.window + 1);
+        const bool skip = t0 > w_last || (p.window > 0 && t0 + PM_BN - 1 < w_first - p.window + 1) ||
+                          t0 + PM_BN - 1 < cs_first;
         if (!skip) {
             float s[PM_BN / 8][4];
 #pragma unroll
@@ -145,7 +150,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
                     }
             }
             const bool need_mask = t0 + PM_BN - 1 > w_first || t0 < lo || t0 + PM_BN > hi ||
-                                   (p.window > 0 && t0 < w_last - p.window + 1);
+                                   (p.window > 0 && t0 < w_last - p.window + 1) || t0 < cs_last;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int nt = 0; nt < PM_BN / 8; ++nt)
@@ -155,7 +160,8 @@ attn_prefill_mma_kernel(const AttnParams p) {
                     if (need_mask) {
                         const int t = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int pos = (e >> 1) ? pos_b : pos_a;
-                        const bool ok = t >= lo && t < hi && t <= pos && (p.window <= 0 || pos - t < p.window);
+                        const bool ok = t >= lo && t < hi && t <= pos && (p.window <= 0 || pos - t < p.window) &&
+                                        t >= ((e >> 1) ? cs_b : cs_a);
                         if (!ok) v = -INFINITY;
                     }
                     s[nt][e] = v;

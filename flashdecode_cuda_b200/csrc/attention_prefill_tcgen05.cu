@@ -213,6 +213,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         p_first[qt] = ctx + first;
         q_hi[qt] = p_first[qt] + nq[qt];
         q_lo[qt] = p.window > 0 ? max(0, p_first[qt] - p.window + 1) : 0;
+        if (p.chunk > 0) q_lo[qt] = max(q_lo[qt], (p_first[qt] / p.chunk) * p.chunk);    // chunked visibility
     }
     const int lo = q_lo[0];
     const int hi = !SPLIT && nq[1] > 0 ? q_hi[1] : q_hi[0];
@@ -383,6 +384,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos = p_first[qt] + r;
         const int my_lo = q_lo[qt], my_hi = q_hi[qt];
+        // chunked visibility: this row's first visible key, and that of the tile's last row
+        const int cs_pos = p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
+        const int cs_last = p.chunk > 0 ? ((p_first[qt] + TA_BM - 1) / p.chunk) * p.chunk : 0;
         const float scale_log2 = p.scale * 1.4426950408889634f;   // > 0: the maximum is taken over raw scores
         float m_run = -INFINITY, l_run = 0.f;                      // running maximum (raw score) and sum
         bool ok = true;
@@ -407,12 +411,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             ta_arrive(ta_saddr(&s_free[qt * 2 + (j & 1)]));
             const bool need_mask = t0 + TA_BN - 1 > p_first[qt] || t0 < my_lo || t0 + TA_BN > my_hi ||
-                                   (p.window > 0 && t0 < p_first[qt] + TA_BM - p.window);
+                                   (p.window > 0 && t0 < p_first[qt] + TA_BM - p.window) || t0 < cs_last;
             if (need_mask) {
 #pragma unroll
                 for (int c = 0; c < TA_BN; ++c) {
                     const int t = t0 + c;
-                    if (!(t >= my_lo && t < my_hi && t <= pos && (p.window <= 0 || pos - t < p.window))) x[c] = -INFINITY;
+                    if (!(t >= my_lo && t < my_hi && t <= pos && t >= cs_pos && (p.window <= 0 || pos - t < p.window))) x[c] = -INFINITY;
                 }
             }
             float mx4[4] = {x[0], x[1], x[2], x[3]};          // four chains instead of one of 63 dependent steps

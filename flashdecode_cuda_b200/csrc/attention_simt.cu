@@ -1,7 +1,9 @@
 // Causal grouped-query attention over the paged KV cache on the CUDA cores,
-// for any head size that is a multiple of 16 (up to 256), any group size up
-// to 64, any block size, an optional sliding window, float or bfloat16
-// storage.  One kernel serves both kinds of step:
+// for any head size that is a multiple of 16 (up to 256; values may have a
+// size of their own), any group size up to 64, any block size, an optional
+// sliding window or chunked visibility (keys of the query's own chunk of
+// `chunk` positions only, chunks counted from the start of the sequence),
+// float or bfloat16 storage.  One kernel serves both kinds of step:
 //
 //  * prompts: a CTA takes QT consecutive query tokens of one sequence and one
 //    KV head, i.e. R = QT * G query rows that share the same keys, and walks
@@ -62,10 +64,11 @@ attn_tile_kernel(const AttnParams p) {
     const int ctx = p.row_ctx_len[b];
     const int tok0 = p.row_q_start[b] + tile * p.QT;       // first query token of this CTA
     const int nq = min(p.QT, q_len - tile * p.QT);
-    const int G = p.G, d = p.d;
+    const int G = p.G, d = p.d, dv = p.dv;
     const int R = nq * G;
     const int p_first = ctx + tile * p.QT;                  // position of the first query token
     int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, (p_first / p.chunk) * p.chunk);   // the earliest chunk start among the tile's queries
     int hi = p_first + nq;                                   // keys 0 .. last query position
     if (p.n_splits > 1) {
         lo = max(lo, split * p.split_len);
@@ -79,8 +82,8 @@ attn_tile_kernel(const AttnParams p) {
     float* p_s = q_s + RMAX * d;                                      // [RMAX][KT]
     float* alpha_s = p_s + RMAX * KT;                                 // [RMAX]
     float* l_s = alpha_s + RMAX;                                      // [RMAX]
-    T* v_s = reinterpret_cast<T*>(l_s + RMAX);                        // [KT][d]
-    T* k_s = v_s + KT * d;                                            // [KT][d + KPAD]
+    T* v_s = reinterpret_cast<T*>(l_s + RMAX);                        // [KT][dv]
+    T* k_s = v_s + KT * dv;                                           // [KT][d + KPAD]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const T* qg = static_cast<const T*>(p.q);
@@ -100,8 +103,9 @@ attn_tile_kernel(const AttnParams p) {
 
     // value phase mapping: a thread owns 4 consecutive dims of several rows
     const int DC = d >> 2;
-    const int RG = ATT_THREADS / DC;
-    const int dc = tid % DC, rg = tid / DC;
+    const int DCV = dv >> 2;
+    const int RG = ATT_THREADS / DCV;
+    const int dc = tid % DCV, rg = tid / DCV;
     const bool pv_active = rg < RG;
     float acc[RPT_MAX][4];
 #pragma unroll
@@ -109,29 +113,34 @@ attn_tile_kernel(const AttnParams p) {
 
     constexpr int EPC = 16 / sizeof(T);          // elements per 16-byte chunk
     const int cpr = d / EPC;                      // chunks per key row
+    const int cprv = dv / EPC;                    // chunks per value row
     const int bs = p.block_size;
 
     for (int t0 = (lo / KT) * KT; t0 < hi; t0 += KT) {
         __syncthreads();   // previous tile consumed (and q_s written, first time round)
         // stage keys and values of this tile; tokens outside [lo, hi) read as zero
-        for (int c = tid; c < KT * cpr; c += ATT_THREADS) {
-            const int tt = c / cpr, cc = c - tt * cpr;
+        for (int c = tid; c < KT * (cpr + cprv); c += ATT_THREADS) {
+            const int tt = c / (cpr + cprv), cc = c - tt * (cpr + cprv);
+            const bool is_v = cc >= cpr;
             const int t = t0 + tt;
-            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+            uint4 x4 = make_uint4(0, 0, 0, 0);
             if (t >= lo && t < hi) {
                 const int blk = p.block_table[(size_t)slot * p.max_blocks + t / bs];
                 if (blk < 0 || blk >= p.num_blocks) {
                     set_status(p.status, STATUS_BAD_BLOCK);
+                } else if (is_v) {
+                    x4 = *reinterpret_cast<const uint4*>(vp + (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * dv + (cc - cpr) * EPC);
                 } else {
-                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * d + cc * EPC;
-                    kv4 = *reinterpret_cast<const uint4*>(kp + off);
-                    vv4 = *reinterpret_cast<const uint4*>(vp + off);
+                    x4 = *reinterpret_cast<const uint4*>(kp + (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * d + cc * EPC);
                 }
             }
-            *reinterpret_cast<uint4*>(v_s + tt * d + cc * EPC) = vv4;
-            uint2* kd = reinterpret_cast<uint2*>(k_s + tt * kstride + cc * EPC);
-            kd[0] = make_uint2(kv4.x, kv4.y);
-            kd[1] = make_uint2(kv4.z, kv4.w);
+            if (is_v) {
+                *reinterpret_cast<uint4*>(v_s + tt * dv + (cc - cpr) * EPC) = x4;
+            } else {
+                uint2* kd = reinterpret_cast<uint2*>(k_s + tt * kstride + cc * EPC);
+                kd[0] = make_uint2(x4.x, x4.y);
+                kd[1] = make_uint2(x4.z, x4.w);
+            }
         }
         __syncthreads();
 
@@ -162,7 +171,8 @@ attn_tile_kernel(const AttnParams p) {
             const int r = warp + i * ATT_WARPS;
             if (r < R) {
                 const int qpos = p_first + r / G;
-                const bool valid = t >= lo && t < hi && t <= qpos && (p.window <= 0 || qpos - t < p.window);
+                const bool valid = t >= lo && t < hi && t <= qpos && (p.window <= 0 || qpos - t < p.window) &&
+                                   (p.chunk <= 0 || t >= (qpos / p.chunk) * p.chunk);
                 const float sv = valid ? s[i] : -INFINITY;
                 const float m_new = fmaxf(m_run[i], warp_max(sv));
                 float pr = 0.f, alpha = 1.f;
@@ -190,7 +200,7 @@ attn_tile_kernel(const AttnParams p) {
             }
             for (int tt = 0; tt < KT; ++tt) {
                 float vf[4];
-                load_chunk4<T>(v_s + tt * d + dc * 4, vf);
+                load_chunk4<T>(v_s + tt * dv + dc * 4, vf);
 #pragma unroll
                 for (int i = 0; i < RPT_MAX; ++i) {
                     const int r = rg + i * RG;
@@ -227,12 +237,12 @@ attn_tile_kernel(const AttnParams p) {
         if (p.n_splits > 1) {
             const size_t pi = row * p.n_splits + split;
             if (dc == 0) { p.part_m[pi] = alpha_s[r]; p.part_l[pi] = l_s[r]; }
-            *reinterpret_cast<float4*>(p.part_acc + pi * d + dc * 4) =
+            *reinterpret_cast<float4*>(p.part_acc + pi * dv + dc * 4) =
                 make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
         } else {
             const float l = l_s[r];
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            T* o = og + row * d + dc * 4;
+            T* o = og + row * dv + dc * 4;
 #pragma unroll
             for (int j = 0; j < 4; ++j) o[j] = from_float<T>(acc[i][j] * inv);
         }
@@ -301,14 +311,14 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
 }
 
 template <typename T>
-static size_t attn_smem_bytes(int d) {
+static size_t attn_smem_bytes(int d, int dv) {
     return (size_t)(RMAX * d + RMAX * KT + 2 * RMAX) * sizeof(float) +
-           (size_t)(KT * d + KT * (d + Pad<T>::v)) * sizeof(T);
+           (size_t)(KT * dv + KT * (d + Pad<T>::v)) * sizeof(T);
 }
 
 template <typename T>
 static int launch_attn(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
-    const size_t smem = attn_smem_bytes<T>(p.d);
+    const size_t smem = attn_smem_bytes<T>(p.d, p.dv);
     auto k = attn_tile_kernel<T>;
     static size_t configured = 0;
     if (smem > configured) {
@@ -330,7 +340,8 @@ typedef __nv_bfloat16 bf16;
 // Largest number of query tokens a CTA takes for a group size (0: unsupported).
 extern "C" int fd_attn_simt_qt(int G) { return G >= 1 && G <= RMAX ? (RMAX / G > 16 ? 16 : RMAX / G) : 0; }
 
-// Floats of scratch the split form needs: part_acc [T, n_q, n_splits, d], then part_m and part_l [T, n_q, n_splits].
+// Floats of scratch the split form needs: part_acc [T, n_q, n_splits, d] (d: the size of a value head), then part_m
+// and part_l [T, n_q, n_splits].
 extern "C" long long fd_attn_scratch_floats(int T, int n_q, int d, int n_splits) {
     return (long long)T * n_q * n_splits * (d + 2);
 }
@@ -344,13 +355,15 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
                           const int* block_table, int max_blocks, int num_blocks, int block_size,
                           const int* tok_row, const int* row_slot, const int* row_q_start,
                           const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
-                          int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                          int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                           int n_splits, int split_len, float* scratch, int* counters, int* status, int use_mma,
                           cudaStream_t stream, const void* prefetch = nullptr, unsigned long long prefetch_bytes = 0) {
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
     FD_REQUIRE(d % 16 == 0 && d >= 16 && d <= 256, -2, "attention: head size %d must be a multiple of 16 in [16, 256]", d);
+    FD_REQUIRE(dv % 16 == 0 && dv >= 16 && dv <= 256, -2, "attention: value head size %d must be a multiple of 16 in [16, 256]", dv);
+    FD_REQUIRE(chunk >= 0 && window >= 0, -2, "attention: chunk %d and window %d must not be negative", chunk, window);
     FD_REQUIRE(G <= RMAX, -2, "attention: group size %d exceeds %d", G, RMAX);
     FD_REQUIRE(block_size > 0, -2, "attention: block size %d", block_size);
     FD_REQUIRE(n_splits >= 1 && n_splits <= COMBINE_MAX_SPLITS, -2, "attention: n_splits=%d (1..%d)", n_splits, COMBINE_MAX_SPLITS);
@@ -369,13 +382,14 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     const size_t n_part = (size_t)T * n_q * n_splits;
     // accumulators first: they are stored as float4 and must stay 16-byte aligned
     p.part_acc = scratch;
-    p.part_m = scratch ? scratch + n_part * d : nullptr;
-    p.part_l = scratch ? scratch + n_part * d + n_part : nullptr;
+    p.part_m = scratch ? scratch + n_part * dv : nullptr;
+    p.part_l = scratch ? scratch + n_part * dv + n_part : nullptr;
     p.block_table = block_table; p.row_slot = row_slot; p.row_q_start = row_q_start;
     p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len; p.status = status;
     p.counters = nullptr;
     p.max_blocks = max_blocks; p.num_blocks = num_blocks; p.block_size = block_size;
-    p.n_q = n_q; p.n_kv = n_kv; p.G = G; p.d = d;
+    p.n_q = n_q; p.n_kv = n_kv; p.G = G; p.d = d; p.dv = dv; p.chunk = chunk;
+    if (dv != d) use_mma = 0;          // the tensor-core kernels keep keys and values of one size
     int qt = fd_attn_simt_qt(G);
     if (qt > max_q_len) qt = max_q_len;
     p.QT = qt; p.n_splits = n_splits; p.split_len = split_len; p.window = window; p.scale = scale;
@@ -399,10 +413,10 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     if (dtype == 0)
         return launch("attention_combine", attn_combine_kernel<float>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
                       (const float*)p.part_m, (const float*)p.part_l, (const float*)p.part_acc, (float*)out, tok_row,
-                      row_slot, n_q, d, n_splits);
+                      row_slot, n_q, dv, n_splits);
     return launch("attention_combine", attn_combine_kernel<bf16>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
                   (const float*)p.part_m, (const float*)p.part_l, (const float*)p.part_acc, (bf16*)out, tok_row,
-                  row_slot, n_q, d, n_splits);
+                  row_slot, n_q, dv, n_splits);
 }
 
 // The CUDA-core kernel for every case.
@@ -410,12 +424,12 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
                                  const int* block_table, int max_blocks, int num_blocks, int block_size,
                                  const int* tok_row, const int* row_slot, const int* row_q_start,
                                  const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
-                                 int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                                 int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                                  int n_splits, int split_len, float* scratch, int* status,
                                  cudaStream_t stream) {
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, n_splits, split_len, scratch, nullptr, status, 0, stream);
+                          window, dv, chunk, n_splits, split_len, scratch, nullptr, status, 0, stream);
 }
 
 // The fastest kernel that takes the sizes: tensor cores where possible.  `counters`
@@ -428,13 +442,13 @@ extern "C" int fd_attention(const void* q, const void* k_pool, const void* v_poo
                             const int* block_table, int max_blocks, int num_blocks, int block_size,
                             const int* tok_row, const int* row_slot, const int* row_q_start,
                             const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
-                            int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                            int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                             int n_splits, int split_len, float* scratch, int* counters, int* status,
                             const void* prefetch, unsigned long long prefetch_bytes, cudaStream_t stream) {
     FD_REQUIRE((uintptr_t)prefetch % 16 == 0, -2, "attention: the memory to prefetch must be 16-byte aligned");
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, n_splits, split_len, scratch, counters, status, 1, stream, prefetch, prefetch_bytes);
+                          window, dv, chunk, n_splits, split_len, scratch, counters, status, 1, stream, prefetch, prefetch_bytes);
 }
 
 // The same without the tcgen05 kernel: prompts go to the mma.sync kernel (head sizes other than 128 always
@@ -443,10 +457,10 @@ extern "C" int fd_attention_mma_sync(const void* q, const void* k_pool, const vo
                                      const int* block_table, int max_blocks, int num_blocks, int block_size,
                                      const int* tok_row, const int* row_slot, const int* row_q_start,
                                      const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
-                                     int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                                     int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                                      int n_splits, int split_len, float* scratch, int* counters, int* status,
                                      cudaStream_t stream) {
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, n_splits, split_len, scratch, counters, status, 2, stream);
+                          window, dv, chunk, n_splits, split_len, scratch, counters, status, 2, stream);
 }

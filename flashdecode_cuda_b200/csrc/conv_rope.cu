@@ -1,0 +1,260 @@
+// Row-wise kernels of mixers that pass their projections through a short causal
+// convolution over time before attention:
+//
+//  * conv_rope_append: for every token of the step, the convolution of each q, k
+//    and v channel over the token's last `taps` projected values (those of
+//    earlier steps come from the sequence's state, zeros before its start), the
+//    rotation of the first `rot` dimensions of every q and k head (dimension i
+//    paired with i + rot/2) at the token's position, q to its buffer and k, v to
+//    the paged cache (value heads may have a size of their own);
+//  * conv_state_update: the sequence's state becomes the last taps - 1 projected
+//    values after the step;
+//  * gate_mul: out = a * sigmoid(g), g read with a row stride (the gate columns
+//    of a packed projection);
+//  * add_concat: [resid + delta | other] as one row, for a product that re-enters
+//    the residual stream;
+//  * relu2: y = max(x, 0)^2.
+//
+// The convolution, the angles' use and the sigmoid are float; storage is float
+// or bfloat16.  The state is float in both.  The k-th tap multiplies the value
+// taps - 1 - k steps back, and the taps are added in the order k = 0, 1, ...:
+// how a prompt was cut into steps changes no bit.
+#include "common.cuh"
+
+namespace fd {
+
+template <typename T>
+__global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                                        float* __restrict__ state, T* __restrict__ q_out,
+                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                        int table_len, int rot, const int* __restrict__ tok_row,
+                                        const int* __restrict__ tok_pos, const int* __restrict__ row_slot,
+                                        const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
+                                        T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                        const int* __restrict__ block_table, int max_blocks, int num_blocks,
+                                        int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
+                                        int update_state, int* status) {
+    extern __shared__ float y_s[];                 // the token's convolved channels [C]
+    const int t = blockIdx.x;
+    const int r = tok_row[t];
+    const int slot = row_slot[r];
+    if (slot < 0) return;                          // padding row
+    const int C = (n_q + n_kv) * d + n_kv * dv;
+    const int q_start = row_q_start[r];
+    const int i = t - q_start;                     // index of the token among the row's new tokens
+    const int pos = tok_pos[t];
+    const int hist = taps - 1;
+    const float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
+
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < taps; ++k) {
+            const int m = i - hist + k;            // index among the row's new tokens of the value this tap sees
+            const float u = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
+                                   : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
+            acc = fmaf(conv_w[(size_t)c * taps + k], u, acc);
+        }
+        y_s[c] = acc;
+    }
+    __syncthreads();
+    // a step of single tokens: this CTA is the only reader of the row's state, so it may move it on
+    if (update_state && state != nullptr && row_q_len[r] == 1) {
+        float* sw = state + (size_t)slot * hist * C;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            for (int s = 0; s + 1 < hist; ++s) sw[(size_t)s * C + c] = sw[(size_t)(s + 1) * C + c];
+            sw[(size_t)(hist - 1) * C + c] = to_float(proj[(size_t)t * ld + c]);
+        }
+    }
+
+    const int half = rot >> 1;
+    bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
+    if (!pos_ok && threadIdx.x == 0) set_status(status, STATUS_BAD_POSITION);
+    const float* cs = cos_t + (size_t)(pos_ok ? pos : 0) * half;
+    const float* sn = sin_t + (size_t)(pos_ok ? pos : 0) * half;
+
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (write_kv && pos >= 0) {
+        const int col = pos / block_size;
+        const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
+        if (blk < 0 || blk >= num_blocks) {
+            if (threadIdx.x == 0) set_status(status, STATUS_BAD_BLOCK);
+        } else {
+            kdst = k_pool + ((size_t)blk * n_kv * block_size + (pos % block_size)) * d;
+            vdst = v_pool + ((size_t)blk * n_kv * block_size + (pos % block_size)) * dv;
+        }
+    }
+    // q and k heads: rotate the leading `rot` dimensions, pass the others on
+    const int n_qk = (n_q + n_kv) * d;
+    for (int e = threadIdx.x; e < n_qk; e += blockDim.x) {
+        const int h = e / d, j = e - h * d;
+        float y = y_s[e];
+        if (j < rot && pos_ok) {
+            if (j < half) y = y * cs[j] - y_s[e + half] * sn[j];
+            else y = y * cs[j - half] + y_s[e - half] * sn[j - half];
+        }
+        if (h < n_q) q_out[(size_t)t * n_q * d + e] = from_float<T>(y);
+        else if (kdst != nullptr) kdst[(size_t)(h - n_q) * block_size * d + j] = from_float<T>(y);
+    }
+    if (vdst != nullptr)
+        for (int e = threadIdx.x; e < n_kv * dv; e += blockDim.x) {
+            const int h = e / dv, j = e - h * dv;
+            vdst[(size_t)h * block_size * dv + j] = from_float<T>(y_s[n_qk + e]);
+        }
+}
+
+// state[slot][s] <- the value (taps - 1 - s) places before the end of the row after this step: one of the step's
+// projected values, or an older entry of the state itself (read before this thread overwrites it: s ascends and the
+// source index s + q_len lies above s).
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state,
+                                         const int* __restrict__ row_slot, const int* __restrict__ row_q_start,
+                                         const int* __restrict__ row_q_len, int C, int hist) {
+    const int r = blockIdx.y;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int q_start = row_q_start[r], q_len = row_q_len[r];
+    float* sw = state + (size_t)slot * hist * C;
+    for (int s = 0; s < hist; ++s) {
+        const int m = q_len - hist + s;
+        sw[(size_t)s * C + c] = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c]) : sw[(size_t)(s + q_len) * C + c];
+    }
+}
+
+template <typename T>
+__global__ void gate_mul_kernel(const T* __restrict__ a, const T* __restrict__ g, int ldg, T* __restrict__ out,
+                                int C, size_t total) {
+    size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; e < total; e += stride) {
+        const size_t m = e / C;
+        const int c = (int)(e - m * C);
+        const float z = to_float(g[m * ldg + c]);
+        out[e] = from_float<T>(to_float(a[e]) / (1.f + expf(-z)));
+    }
+}
+
+template <typename TD, typename T>
+__global__ void add_concat_kernel(const TD* __restrict__ delta, float* __restrict__ resid,
+                                  const float* __restrict__ other, T* __restrict__ out, int H) {
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = resid[t * H + i];
+        if (delta != nullptr) {
+            x += to_float(delta[t * H + i]);
+            resid[t * H + i] = x;
+        }
+        out[t * 2 * H + i] = from_float<T>(x);
+        out[t * 2 * H + H + i] = from_float<T>(other[t * H + i]);
+    }
+}
+
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, size_t total) {
+    size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; e < total; e += stride) {
+        const float v = fmaxf(to_float(x[e]), 0.f);
+        out[e] = from_float<T>(v * v);
+    }
+}
+
+static int grid_for(size_t total, int threads) {
+    const size_t b = (total + threads - 1) / threads;
+    return (int)(b < 148 * 16 ? b : 148 * 16);
+}
+
+}  // namespace fd
+
+using namespace fd;
+typedef __nv_bfloat16 bf16;
+
+// dtype (0 float32, 1 bfloat16): type of proj, q_out and the cache.  proj [T, ld] holds q (n_q * d columns), k
+// (n_kv * d) and v (n_kv * dv) side by side from column 0; conv_w [C, taps] and state [slots, taps - 1, C] are float
+// (state may be null when taps == 1).  cos_t / sin_t [table_len, rot / 2] (unused when rot == 0).
+// update_state != 0: rows that bring one token move their state on here; other rows need fd_conv_state_update.
+extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const float* conv_w, float* state, void* q_out,
+                                   const float* cos_t, const float* sin_t, int table_len, int rot,
+                                   const int* tok_row, const int* tok_pos, const int* row_slot,
+                                   const int* row_q_start, const int* row_q_len, void* k_pool, void* v_pool,
+                                   const int* block_table, int max_blocks, int num_blocks, int block_size, int T,
+                                   int n_q, int n_kv, int d, int dv, int taps, int write_kv, int update_state,
+                                   int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    FD_REQUIRE(n_q > 0 && n_kv > 0 && d > 0 && dv > 0 && taps >= 1 && block_size > 0, -2, "conv_rope_append: bad sizes");
+    FD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, -2, "conv_rope_append: %d rotated dimensions of a head of %d", rot, d);
+    FD_REQUIRE(taps == 1 || state != nullptr, -2, "conv_rope_append: %d taps need a state", taps);
+    const int C = (n_q + n_kv) * d + n_kv * dv;
+    FD_REQUIRE(ld >= C, -2, "conv_rope_append: rows of %d columns cannot hold %d channels", ld, C);
+    const size_t smem = (size_t)C * sizeof(float);
+    FD_REQUIRE(smem <= 200 * 1024, -2, "conv_rope_append: %d channels need %zu bytes of shared memory (max 200 KB)", C, smem);
+    const int threads = C >= 1024 ? 256 : 128;
+    if (dtype == 0) {
+        auto k = conv_rope_append_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return launch("conv_rope_append", k, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1), (const float*)proj, ld,
+                      conv_w, state, (float*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
+                      row_q_len, (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q,
+                      n_kv, d, dv, taps, write_kv, update_state, status);
+    }
+    auto k = conv_rope_append_kernel<bf16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch("conv_rope_append", k, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1), (const bf16*)proj, ld,
+                  conv_w, state, (bf16*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
+                  row_q_len, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv,
+                  d, dv, taps, write_kv, update_state, status);
+}
+
+extern "C" int fd_conv_state_update(const void* proj, int ld, int dtype, float* state, const int* row_slot,
+                                    const int* row_q_start, const int* row_q_len, int n_rows, int C, int taps,
+                                    cudaStream_t stream) {
+    if (n_rows == 0 || taps <= 1) return 0;
+    FD_REQUIRE(state != nullptr && C > 0 && ld >= C, -2, "conv_state_update: bad arguments");
+    FD_REQUIRE(n_rows <= 65535, -2, "conv_state_update: batch of %d rows too large", n_rows);
+    dim3 grid((C + 127) / 128, n_rows);
+    if (dtype == 0)
+        return launch("conv_state_update", conv_state_update_kernel<float>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
+                      (const float*)proj, ld, state, row_slot, row_q_start, row_q_len, C, taps - 1);
+    return launch("conv_state_update", conv_state_update_kernel<bf16>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)proj, ld, state, row_slot, row_q_start, row_q_len, C, taps - 1);
+}
+
+// out[m, c] = a[m, c] * sigmoid(g[m * ldg + c]) for M rows of C columns.
+extern "C" int fd_gate_mul(const void* a, const void* g, int ldg, void* out, int dtype, int M, int C, cudaStream_t stream) {
+    const size_t total = (size_t)M * C;
+    if (total == 0) return 0;
+    if (dtype == 0)
+        return launch("gate_mul", gate_mul_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, stream, dim3(1, 1, 1),
+                      (const float*)a, (const float*)g, ldg, (float*)out, C, total);
+    return launch("gate_mul", gate_mul_kernel<bf16>, dim3(grid_for(total, 256)), dim3(256), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)a, (const bf16*)g, ldg, (bf16*)out, C, total);
+}
+
+// resid += delta (delta may be null); out[t] = [resid[t] | other[t]] in the type `dtype`.
+// delta_dtype: 0 float32, 1 bfloat16.
+extern "C" int fd_add_concat(const void* delta, int delta_dtype, float* resid, const float* other, void* out, int dtype,
+                             int T, int H, cudaStream_t stream) {
+    if (T == 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+#define FD_AC(TD_, T_)                                                                                         \
+    return launch("add_concat", add_concat_kernel<TD_, T_>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), \
+                  (const TD_*)delta, resid, other, (T_*)out, H)
+    if (dtype == 0) {
+        if (delta_dtype == 0) FD_AC(float, float);
+        FD_AC(bf16, float);
+    }
+    if (delta_dtype == 0) FD_AC(float, bf16);
+    FD_AC(bf16, bf16);
+#undef FD_AC
+}
+
+extern "C" int fd_relu2(const void* x, void* out, int dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (dtype == 0)
+        return launch("relu2", relu2_kernel<float>, dim3(grid_for((size_t)total, 256)), dim3(256), 0, stream,
+                      dim3(1, 1, 1), (const float*)x, (float*)out, (size_t)total);
+    return launch("relu2", relu2_kernel<bf16>, dim3(grid_for((size_t)total, 256)), dim3(256), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)x, (bf16*)out, (size_t)total);
+}

@@ -68,9 +68,11 @@ class RunSpec:
     ``ModelBlueprint.layers`` (a layer may be named by several entries: its
     weights are shared, its cache is not).  ``cache_from``: index of an EARLIER
     entry whose keys/values and state this entry reads instead of keeping its
-    own."""
+    own.  ``before``: name of a stream operation (``ModelBlueprint.stream_ops``)
+    that rewrites the residual stream right before this entry's layer runs."""
     layer: int
     cache_from: Optional[int] = None
+    before: Optional[str] = None
 
 
 @dataclass
@@ -84,9 +86,14 @@ class ModelBlueprint:
     final_norm: PartSpec
     head: PartSpec
     max_positions: int                        # longest sequence the configuration allows
+    # operations on the whole residual stream between layers, by the name schedule entries ask for
+    stream_ops: Dict[str, PartSpec] = field(default_factory=dict)
 
     def validate(self) -> None:
         for i, run in enumerate(self.schedule):
+            if run.before is not None and run.before not in self.stream_ops:
+                raise ValueError(f"schedule entry {i} names the stream operation {run.before!r}, "
+                                 f"the model has {sorted(self.stream_ops)}")
             if not (0 <= run.layer < len(self.layers)):
                 raise ValueError(f"schedule entry {i} names layer {run.layer}, the model has {len(self.layers)}")
             if run.cache_from is not None:

@@ -146,6 +146,7 @@ class Model:
             self.blocks.append(block_cls(**{name: self._build(spec) for name, spec in ls.parts.items()}))
         self.final_norm = self._build(blueprint.final_norm)
         self.head = self._build(blueprint.head)
+        self.stream_ops = {name: self._build(spec) for name, spec in blueprint.stream_ops.items()}
         self.schedule = list(blueprint.schedule)
         self._layout = self._cache_layout()
         self.rt: Optional[Runtime] = None
@@ -174,7 +175,7 @@ class Model:
         parts = list(self.positions.values()) + [self.embedding]
         for b in self.blocks:
             parts += [b] + list(b.parts())
-        return parts + [self.final_norm, self.head]
+        return parts + list(self.stream_ops.values()) + [self.final_norm, self.head]
 
     def tensor_specs(self) -> List[W.TensorSpec]:
         specs, seen = [], set()
@@ -229,7 +230,7 @@ class Model:
 
     # ------------------------------------------------------------------ cache
     def _cache_layout(self):
-        groups: List[dict] = []          # {"key": (n_kv, d, window), "n_layers": int}
+        groups: List[dict] = []          # {"key": (n_kv, d, window, chunk, value size), "n_layers": int}
         states: List[StateSpec] = []
         runs = []                        # per schedule entry: (group index or None, layer in group, writes, {name: state key})
         for i, run in enumerate(self.schedule):
@@ -239,9 +240,7 @@ class Model:
                 owner = self.schedule[run.cache_from]
                 omixer = getattr(self.blocks[owner.layer], "mixer", None)
                 oreq = omixer.kv_request() if omixer is not None else None
-                if (req is None) != (oreq is None) or (req is not None and
-                                                       (req.n_kv_heads, req.head_dim, req.window) !=
-                                                       (oreq.n_kv_heads, oreq.head_dim, oreq.window)):
+                if (req is None) != (oreq is None) or (req is not None and req.key() != oreq.key()):
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {run.cache_from}: "
                                      f"their mixers keep different things")
                 g, l, _, st = runs[run.cache_from]
@@ -249,7 +248,7 @@ class Model:
                 continue
             gi, li = None, 0
             if req is not None:
-                key = (req.n_kv_heads, req.head_dim, req.window)
+                key = req.key()
                 for j, g in enumerate(groups):
                     if g["key"] == key:
                         gi = j
@@ -388,17 +387,27 @@ class Model:
         self.embedding.forward(ctx, resid)
         if self.trace is not None:
             self.trace["embed"] = resid.detach().float().cpu().clone()
+        embedded = None
+        if self.stream_ops:
+            # stream operations may read the embedding output again later in the step
+            embedded = ctx.ws.get("embedded", (ctx.T, self.hidden_size), torch.float32)
+            embedded.copy_(resid)
         caches = self._layer_caches(ctx.cache)
         delta = None
         for i, run in enumerate(self.schedule):
+            if run.before is not None:
+                # the operation adds the pending delta itself and leaves the new stream in resid
+                delta = self.stream_ops[run.before].forward(ctx, resid, delta, embedded)
             # whoever norms next - the next entry's block or the final norm - says whether it takes float
             # partial sums [parts, T, H] for a delta; a block hands that on to its last sub-layer
-            nxt = self.blocks[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else self.final_norm
-            ctx.delta_parts_ok = bool(getattr(nxt, "accepts_parts", False))
-            ctx.upcoming = (nxt if i + 1 < len(self.schedule) else self.head).first_weights()
+            last = i + 1 >= len(self.schedule)
+            nxt = self.final_norm if last else self.blocks[self.schedule[i + 1].layer]
+            op_next = None if last or self.schedule[i + 1].before is None else self.stream_ops[self.schedule[i + 1].before]
+            ctx.delta_parts_ok = bool(getattr(op_next if op_next is not None else nxt, "accepts_parts", False))
+            ctx.upcoming = (op_next if op_next is not None else (self.head if last else nxt)).first_weights()
             delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[i])
             if self.trace is not None:
-                d = delta.float().sum(0) if delta.dim() == 3 else delta.float()
+                d = 0 if delta is None else (delta.float().sum(0) if delta.dim() == 3 else delta.float())
                 self.trace[f"layer.{i}"] = (resid + d).cpu()
         if ctx.n_want == 0:
             return None

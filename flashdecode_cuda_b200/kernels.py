@@ -92,9 +92,19 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P, c_ulonglong, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
         "fd_attn_simt_qt": [I],
-        "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
-        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P, c_ulonglong, P],
-        "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
+        "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P],
+        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P, c_ulonglong, P],
+        "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P],
+        "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
+        "fd_conv_state_update": [P, I, I, P, P, P, P, I, I, I, P],
+        "fd_gate_mul": [P, P, I, P, I, I, I, P],
+        "fd_add_concat": [P, I, P, P, P, I, I, I, P],
+        "fd_relu2": [P, P, I, LL, P],
+        "fd_moe_tile_rows": [],
+        "fd_moe_route": [P, P, I, P, P, P, I, I, I, I, P],
+        "fd_moe_align": [P, I, I, P, P, P, P, I, P],
+        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, P],
+        "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
         "fd_copy_d2h_sync": [P, P, LL, P],
@@ -466,17 +476,19 @@ def _counters(device, n: int) -> torch.Tensor:
 
 def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
                row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
-               scratch, status, prefetch=None, prefetch_bytes=0) -> None:
+               scratch, status, prefetch=None, prefetch_bytes=0, chunk=0) -> None:
     T = q.shape[0]
     num_blocks, _, block_size, _ = k_pool.shape
-    assert q.dtype == k_pool.dtype == out.dtype
+    v_dim = v_pool.shape[-1]
+    assert q.dtype == k_pool.dtype == out.dtype and k_pool.shape[-1] == head_dim and out.shape[-1] == n_q * v_dim
+    assert v_pool.shape[:3] == k_pool.shape[:3]
     if n_splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32
-        assert scratch.numel() >= attention_scratch_floats(T, n_q, head_dim, n_splits)
+        assert scratch.numel() >= attention_scratch_floats(T, n_q, v_dim, n_splits)
     args = [_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype), _ptr(block_table), block_table.shape[1],
             num_blocks, block_size, _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
-            _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), n_splits,
-            split_len, _ptr(scratch)]
+            _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), int(v_dim),
+            int(chunk), n_splits, split_len, _ptr(scratch)]
     if fn_name != "fd_attention_simt":
         fused = n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16
         args.append(_ptr(_counters(q.device, n_rows * n_kv)) if fused else None)
@@ -493,15 +505,18 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
               n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
               window: int = 0, n_splits: int = 1, split_len: int = 0,
               scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-              prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 0) -> None:
+              prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 0, chunk: int = 0) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     fastest kernel that takes the sizes (tensor cores for bfloat16 decode steps
-    with head size 64 or 128; the CUDA-core kernel otherwise).  ``prefetch``: a
+    with head size 64 or 128; the CUDA-core kernel otherwise).  ``window`` > 0: a query
+    sees the last ``window`` keys only; ``chunk`` > 0: only the keys of its own chunk of
+    ``chunk`` positions, counted from the start of the sequence.  The size of a value head
+    is that of ``v_pool`` (the tensor-core kernels take it equal to the key's).  ``prefetch``: a
     tensor that a later kernel streams; the tensor-core decode kernel asks L2 for its
     first ``prefetch_bytes`` when its own reads are through (the other kernels do not)."""
     _attention("fd_attention", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
                row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
-               scratch, status, prefetch, prefetch_bytes)
+               scratch, status, prefetch, prefetch_bytes, chunk=chunk)
 
 
 def attention_mma_sync(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
@@ -509,12 +524,13 @@ def attention_mma_sync(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
                        row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
                        n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
                        window: int = 0, n_splits: int = 1, split_len: int = 0,
-                       scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+                       scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                       chunk: int = 0) -> None:
     """The same with prompts on the mma.sync kernel even at head size 128, where
     ``attention`` takes the tcgen05 kernel."""
     _attention("fd_attention_mma_sync", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start,
                row_q_len, row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits,
-               split_len, scratch, status)
+               split_len, scratch, status, chunk=chunk)
 
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
@@ -522,11 +538,139 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                    row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
                    n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
                    window: int = 0, n_splits: int = 1, split_len: int = 0,
-                   scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+                   scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                   chunk: int = 0) -> None:
     """The same on the CUDA cores for every size (the true 32-bit path)."""
     _attention("fd_attention_simt", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start,
                row_q_len, row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits,
-               split_len, scratch, status)
+               split_len, scratch, status, chunk=chunk)
+
+
+# ---------------------------------------------------------------------------
+# short convolution + partial rotation + cache append; gates; routed experts
+
+def conv_rope_append(proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[torch.Tensor], q_out: torch.Tensor,
+                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dims: int, tok_row: torch.Tensor,
+                     tok_pos: torch.Tensor, row_slot: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
+                     k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int,
+                     head_dim: int, v_head_dim: int, write_kv: bool, update_state: bool, status: torch.Tensor) -> None:
+    """For every token: the causal convolution over time of each q, k and v channel of ``proj``
+    [T, >= C] (C = (n_q + n_kv) head_dim + n_kv v_head_dim leading columns) with ``conv_w`` [C, taps]
+    (float32), earlier steps' values taken from ``state`` [slots, taps - 1, C] (float32); rotation of
+    the first ``rot_dims`` dimensions of every q and k head (i paired with i + rot_dims / 2); q to
+    ``q_out`` [T, n_q head_dim], k and v to the paged pools.  ``update_state``: rows that bring one
+    token move their state on in the same kernel (use ``conv_state_update`` for the others)."""
+    T = proj.shape[0]
+    taps = conv_w.shape[1]
+    C = (n_q + n_kv) * head_dim + n_kv * v_head_dim
+    assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and proj.shape[1] >= C
+    assert state is None or (state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C))
+    assert proj.dtype == q_out.dtype == k_pool.dtype == v_pool.dtype and q_out.shape == (T, n_q * head_dim)
+    assert k_pool.shape[-1] == head_dim and v_pool.shape[-1] == v_head_dim
+    if rot_dims:
+        assert cos.dtype == torch.float32 and cos.shape[1] == rot_dims // 2 and sin.shape == cos.shape
+    num_blocks, _, block_size, _ = k_pool.shape
+    _check(lib().fd_conv_rope_append(_ptr(proj), proj.shape[1], _dt(proj.dtype), _ptr(conv_w), _ptr(state), _ptr(q_out),
+                                     _ptr(cos) if rot_dims else None, _ptr(sin) if rot_dims else None,
+                                     cos.shape[0] if rot_dims else 0, rot_dims, _ptr(tok_row), _ptr(tok_pos),
+                                     _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(k_pool), _ptr(v_pool),
+                                     _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, n_q, n_kv,
+                                     head_dim, v_head_dim, taps, int(write_kv), int(update_state), _ptr(status),
+                                     _stream()))
+
+
+def conv_state_update(proj: torch.Tensor, state: torch.Tensor, row_slot: torch.Tensor, row_q_start: torch.Tensor,
+                      row_q_len: torch.Tensor, n_rows: int) -> None:
+    """``state`` [slots, taps - 1, C] of every row's sequence <- its last taps - 1 projected values after the step."""
+    hist, C = state.shape[1], state.shape[2]
+    assert state.dtype == torch.float32 and proj.shape[1] >= C
+    _check(lib().fd_conv_state_update(_ptr(proj), proj.shape[1], _dt(proj.dtype), _ptr(state), _ptr(row_slot),
+                                      _ptr(row_q_start), _ptr(row_q_len), n_rows, C, hist + 1, _stream()))
+
+
+def gate_mul(a: torch.Tensor, packed: torch.Tensor, first_col: int, out: torch.Tensor) -> None:
+    """out = a * sigmoid(g) with g the columns ``first_col ...`` of ``packed`` [M, ld]; a, out [M, C]."""
+    M, C = a.shape
+    assert out.shape == a.shape and a.dtype == out.dtype == packed.dtype and packed.shape[0] == M
+    assert first_col + C <= packed.shape[1] and packed.is_contiguous()
+    g_ptr = packed.data_ptr() + first_col * packed.element_size()
+    _check(lib().fd_gate_mul(_ptr(a), g_ptr, packed.shape[1], _ptr(out), _dt(a.dtype), M, C, _stream()))
+
+
+def add_concat(delta: Optional[torch.Tensor], resid: torch.Tensor, other: torch.Tensor, out: torch.Tensor) -> None:
+    """resid += delta (if given); out [T, 2H] = [resid | other] in out's dtype; resid and other float32 [T, H]."""
+    T, H = resid.shape
+    assert resid.dtype == other.dtype == torch.float32 and out.shape == (T, 2 * H) and other.shape == resid.shape
+    assert delta is None or delta.shape == resid.shape
+    _check(lib().fd_add_concat(_ptr(delta), _dt(delta.dtype) if delta is not None else 0, _ptr(resid), _ptr(other),
+                               _ptr(out), _dt(out.dtype), T, H, _stream()))
+
+
+def relu2(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(x, 0)^2."""
+    assert x.shape == out.shape and x.dtype == out.dtype
+    _check(lib().fd_relu2(_ptr(x), _ptr(out), _dt(x.dtype), x.numel(), _stream()))
+
+
+def moe_tile_rows() -> int:
+    return int(lib().fd_moe_tile_rows())
+
+
+def moe_grouped_rows(n_pairs: int, n_experts: int) -> int:
+    """Rows of the grouped buffers that hold ``n_pairs`` (token, choice) pairs of ``n_experts`` experts whatever the
+    routing: every expert's group is padded to whole tiles."""
+    mt = moe_tile_rows()
+    worst = n_pairs + min(n_experts, n_pairs) * (mt - 1)
+    return -(-worst // mt) * mt
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
+              wts: torch.Tensor) -> None:
+    """Per row of x [T, H]: softmax scores over the rows of ``router`` [n_out, H] (float arithmetic), the ``top``
+    outputs with the largest score + correction into ``ids`` [T, top] (int32), and their scores over their sum
+    (+ 1e-20) into ``wts`` [T, top] (float32)."""
+    T, H = x.shape
+    n_out, top = router.shape[0], ids.shape[1]
+    assert router.shape == (n_out, H) and router.dtype == x.dtype and ids.dtype == torch.int32
+    assert wts.dtype == torch.float32 and wts.shape == ids.shape == (T, top)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n_out)
+    _check(lib().fd_moe_route(_ptr(x), _ptr(router), _dt(x.dtype), _ptr(correction), _ptr(ids), _ptr(wts), T, H, n_out,
+                              top, _stream()))
+
+
+def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_pair: torch.Tensor,
+              tile_expert: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Group the (token, choice) pairs of ``ids`` by expert (outputs >= ``n_experts`` are left out: pair_pos -1)."""
+    P = ids.numel()
+    cap = sorted_pair.numel()
+    assert all(t.dtype == torch.int32 for t in (ids, pair_pos, sorted_pair, tile_expert, n_tiles))
+    assert pair_pos.numel() >= P and tile_expert.numel() * moe_tile_rows() >= cap
+    _check(lib().fd_moe_align(_ptr(ids), P, n_experts, _ptr(pair_pos), _ptr(sorted_pair), _ptr(tile_expert),
+                              _ptr(n_tiles), cap, _stream()))
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, sorted_pair: torch.Tensor,
+             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int) -> None:
+    """Grouped product with the experts' stacked matrices w [E, N, K].  ``down`` False: a = x [T, K] (rows gathered
+    through the grouping), out [cap, N] = relu(x w_e^T)^2 in a's dtype; True: a = the grouped activations [cap, K],
+    out [cap, N] float32."""
+    E, N, Kd = w.shape
+    cap = sorted_pair.numel()
+    assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N)
+    assert out.dtype == (torch.float32 if down else a.dtype) and (not down or a.shape[0] == cap)
+    _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), int(down), _ptr(sorted_pair), _ptr(tile_expert),
+                             _ptr(n_tiles), cap, top, N, Kd, _stream()))
+
+
+def moe_combine(y: Optional[torch.Tensor], x: torch.Tensor, shared: Optional[torch.Tensor], ids: torch.Tensor,
+                wts: torch.Tensor, pair_pos: torch.Tensor, out: torch.Tensor, n_experts: int) -> None:
+    """out[t] = sum_c wts[t, c] * (y[pair_pos[t, c]] if ids[t, c] < n_experts else x[t]) + shared[t]."""
+    T, H = x.shape
+    top = ids.shape[1]
+    assert out.shape == x.shape and out.dtype == x.dtype and (shared is None or shared.shape == x.shape)
+    assert y is None or (y.dtype == torch.float32 and y.shape[1] == H)
+    _check(lib().fd_moe_combine(_ptr(y), _ptr(x), _ptr(shared), _ptr(ids), _ptr(wts), _ptr(pair_pos), _ptr(out),
+                                _dt(x.dtype), T, H, top, n_experts, _stream()))
 
 
 _sample_scratch = {}

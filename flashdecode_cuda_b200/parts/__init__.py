@@ -1,7 +1,7 @@
 """The parts a model is put together from.  Importing this package registers
-the parts of the Qwen2 dense decoder."""
+the parts of the architectures this library ships."""
 
-from . import attention, block, embedding, head, mlp, norm, rope  # noqa: F401  (registration)
+from . import attention, block, conv_attention, embedding, head, mlp, moe, norm, rope, stream  # noqa: F401  (registration)
 from .base import (Block, Embedding, FeedForward, Head, KVRequest, LayerCache, Mixer, Norm, Part, Position,
                    Runtime)
 

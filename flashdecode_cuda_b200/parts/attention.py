@@ -49,12 +49,14 @@ class GQAAttention(Mixer):
     Formulas: engine/model.py:188-208,273-293 and engine/ops.py:153-194 of
     davidjoyme/flashdecode-cuda; query head h reads KV head h // G; scale
     1/sqrt(head_dim).  ``window``: a query sees only the last ``window`` keys.
+    ``chunk``: a query sees only the keys of its own chunk of ``chunk`` positions.
     ``bias``: True = required, False = refused, None = taken if the checkpoint
     has it (the reference's rule, engine/loader.py:29-33).
     """
 
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                 position: "RotaryHalf", window: Optional[int] = None, bias: Optional[bool] = None):
+                 position: "RotaryHalf", window: Optional[int] = None, bias: Optional[bool] = None,
+                 chunk: Optional[int] = None):
         if head_dim < 16 or head_dim > 256 or head_dim % 16 != 0:
             raise ValueError(f"{prefix}: head size {head_dim} is not taken: the attention kernels take multiples of 16 "
                              f"from 16 to 256")
@@ -63,7 +65,7 @@ class GQAAttention(Mixer):
                              f"groups of up to 64 query heads per key/value head")
         self.prefix = prefix
         self.hidden_size, self.n_q, self.n_kv, self.d = hidden_size, n_heads, n_kv_heads, head_dim
-        self.position, self.window, self.bias = position, window, bias
+        self.position, self.window, self.bias, self.chunk = position, window, bias, chunk
         self.scale = 1.0 / math.sqrt(head_dim)
 
     # --- what it needs -------------------------------------------------
@@ -81,7 +83,7 @@ class GQAAttention(Mixer):
         return specs
 
     def kv_request(self) -> KVRequest:
-        return KVRequest(self.n_kv, self.d, self.window)
+        return KVRequest(self.n_kv, self.d, self.window, self.chunk)
 
     def _paired_order(self) -> torch.Tensor:
         """Row order of the packed q/k/v matrix: inside every q and k head, tiles
@@ -172,6 +174,6 @@ class GQAAttention(Mixer):
         K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot,
                          ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len,
                          self.n_q, self.n_kv, d, self.scale, self.window or 0, n_splits, split_len, scratch,
-                         self.rt.status, prefetch=ahead, prefetch_bytes=UPCOMING_BYTES)
+                         self.rt.status, prefetch=ahead, prefetch_bytes=UPCOMING_BYTES, chunk=self.chunk or 0)
         out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
         return matmul(attn, self.w_o, None, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status)

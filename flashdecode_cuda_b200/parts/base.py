@@ -55,10 +55,18 @@ class Runtime:
 
 @dataclass
 class KVRequest:
-    """Paged key/value storage a mixer needs for each sequence."""
+    """Paged key/value storage a mixer needs for each sequence.  ``window``: only the last
+    so many keys are ever read; ``chunk``: only the keys of the query's own chunk of so many
+    positions; ``v_head_dim``: size of a value head where it differs from ``head_dim``."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    def key(self):
+        v = None if self.v_head_dim in (None, self.head_dim) else self.v_head_dim
+        return (self.n_kv_heads, self.head_dim, self.window, self.chunk, v)
 
 
 @dataclass

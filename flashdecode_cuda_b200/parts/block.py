@@ -18,14 +18,18 @@ class PreNormBlock(Block):
     previous sub-layer's output to the residual stream, so add and norm are one
     kernel (the threading of engine/model.py:173-184,210-212 in
     davidjoyme/flashdecode-cuda).  Returns the feed-forward's output, still to
-    be added by whoever norms next.
+    be added by whoever norms next.  A layer without a feed-forward
+    (``feed_forward`` None) is x += mixer(norm1(x)) alone; a ``norm2`` it is
+    given all the same declares its tensor and never runs.
     """
 
-    def __init__(self, norm1, mixer, norm2, feed_forward):
+    def __init__(self, norm1, mixer, norm2=None, feed_forward=None):
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        if feed_forward is not None and norm2 is None:
+            raise ValueError("a pre-norm layer with a feed-forward needs its second norm")
 
     def parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.feed_forward]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
 
     def first_weights(self) -> Optional[torch.Tensor]:
         return self.mixer.first_weights()
@@ -39,6 +43,8 @@ class PreNormBlock(Block):
         xn = ctx.ws.get("normed", tuple(resid.shape), ctx.rt.dtype)
         after_block = ctx.upcoming                       # what the step streams after this block (set by the model)
         self.norm1.forward(ctx, delta, resid, xn)
+        if self.feed_forward is None:
+            return self.mixer.forward(ctx, xn, lc)
         ctx.upcoming = self.feed_forward.first_weights()
         d1 = self.mixer.forward(ctx, xn, lc)
         self.norm2.forward(ctx, d1, resid, xn)

@@ -1,0 +1,134 @@
+"""Attention whose q, k and v pass through a short causal convolution over time,
+with a partial rotation, chunked visibility and a sigmoid gate on the output."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..cache.paged import StateSpec
+from ..registry import register_part
+from ..weights.spec import TensorSpec
+from .attention import FP32_SPLIT_LEN, plan_splits
+from .base import KVRequest, LayerCache, Mixer, Runtime
+from .linear import matmul
+
+
+@register_part("mixer", "conv_gated_attention")
+class ConvGatedAttention(Mixer):
+    """For the mixer's input h [T, hidden]:
+
+        q, k, v = W_q h, W_k h, W_v h                     (no biases)
+        u_t     = sum_j c[:, j] * u_(t - taps + 1 + j)    per channel of q, k and v; zeros before the sequence
+        q, k    = rotation of the first ``rot_dims`` dimensions of every head (i paired with i + rot_dims / 2,
+                  angle position * base^(-2i / rot_dims)); the other dimensions pass
+        a       = softmax over the visible keys of (q . k) * scale; grouped heads: query head h reads
+                  key/value head h // (n_heads / n_kv_heads); value heads have ``v_head_dim`` dimensions
+        out     = W_o (a * sigmoid(W_g h))                (``gate`` False: no gate)
+
+    Visible keys of the query at position i: j <= i, of the last ``window`` positions if a window is given, and
+    of i's own chunk (i // chunk == j // chunk) if a chunk is given.
+
+    The last ``taps - 1`` projected values (before the convolution) of every sequence are its state, kept in
+    float32 per cache slot; keys (rotated) and values (both after the convolution) go to the paged cache.
+    One packed product gives q, k, v and the gate.  Tensors: ``<prefix>.q`` / ``.k`` / ``.v`` / ``.g`` / ``.o``
+    (stored [out, in]) and ``<prefix>.q.conv`` / ``.k.conv`` / ``.v.conv`` ([channels, taps]).
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
+                 taps: int, scale: float, position=None, rot_dims: int = 0, chunk: Optional[int] = None,
+                 window: Optional[int] = None, gate: bool = True):
+        for what, n in (("head size", head_dim), ("value head size", v_head_dim)):
+            if n < 16 or n > 256 or n % 16 != 0:
+                raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take multiples of 16 "
+                                 f"from 16 to 256")
+        if n_kv_heads < 1 or n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 64:
+            raise ValueError(f"{prefix}: {n_heads} query heads for {n_kv_heads} key/value heads: the kernels take whole "
+                             f"groups of up to 64 query heads per key/value head")
+        if taps < 1 or rot_dims < 0 or rot_dims % 2 or rot_dims > head_dim or (rot_dims and position is None):
+            raise ValueError(f"{prefix}: {taps} taps, {rot_dims} rotated dimensions of {head_dim}: taps must be "
+                             f"positive, the rotated dimensions even, at most the head size and given a position part")
+        self.prefix = prefix
+        self.hidden_size, self.n_q, self.n_kv, self.d, self.dv = hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim
+        self.taps, self.scale, self.position, self.rot_dims = taps, float(scale), position, rot_dims
+        self.chunk, self.window, self.gate = chunk, window, gate
+        self.n_conv = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim     # channels that are convolved
+
+    # --- what it needs -------------------------------------------------
+    def _sizes(self):
+        return (("q", self.n_q * self.d), ("k", self.n_kv * self.d), ("v", self.n_kv * self.dv))
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        specs = []
+        for n, c in self._sizes():
+            specs.append(TensorSpec(f"{p}.{n}", (c, H), init="unit"))
+            specs.append(TensorSpec(f"{p}.{n}.conv", (c, self.taps), "vector", init="conv"))
+        if self.gate:
+            specs.append(TensorSpec(f"{p}.g", (self.n_q * self.dv, H), init="unit"))
+        specs.append(TensorSpec(f"{p}.o", (H, self.n_q * self.dv), init="unit"))
+        return specs
+
+    def kv_request(self) -> KVRequest:
+        return KVRequest(self.n_kv, self.d, self.window, self.chunk, self.dv)
+
+    def state_requests(self) -> List[StateSpec]:
+        if self.taps == 1:
+            return []
+        return [StateSpec("conv", (self.taps - 1, self.n_conv), torch.float32)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        mats = [tensors.pop(f"{p}.{n}") for n, _ in self._sizes()]
+        if self.gate:
+            mats.append(tensors.pop(f"{p}.g"))
+        self.w_in = torch.cat(mats, dim=0).contiguous()            # [q | k | v | gate] rows: one product
+        self.conv_w = torch.cat([tensors.pop(f"{p}.{n}.conv").float() for n, _ in self._sizes()], dim=0).contiguous()
+        self.w_o = tensors[f"{p}.o"]
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() * self.w_in.element_size() + self.w_o.numel() * self.w_o.element_size()
+                + self.conv_w.numel() * 4)
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_in
+
+    # --- a step ----------------------------------------------------------
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, ws, rt = ctx.T, ctx.ws, self.rt
+        proj = ws.get("cga_proj", (T, self.w_in.shape[0]), x.dtype)
+        matmul(x, self.w_in, None, proj, status=rt.status)
+        q = ws.get("cga_q", (T, self.n_q * self.d), x.dtype)
+        state = lc.states.get("conv")
+        rope = self.position
+        single = ctx.max_q_len == 1                     # every row brings one token: the state moves on in the same kernel
+        K.conv_rope_append(proj, self.conv_w, state, q, rope.cos if self.rot_dims else None,
+                           rope.sin if self.rot_dims else None, self.rot_dims, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
+                           ctx.row_q_start, ctx.row_q_len, lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv,
+                           self.d, self.dv, lc.writes, single and lc.writes, rt.status)
+        if state is not None and lc.writes and not single:
+            K.conv_state_update(proj, state, ctx.row_slot, ctx.row_q_start, ctx.row_q_len, ctx.n_rows)
+        attn = ws.get("cga_attn", (T, self.n_q * self.dv), x.dtype)
+        n_splits, split_len, scratch = 1, 0, None
+        if single:
+            if x.dtype == torch.float32:
+                # splits of a fixed length: where a sequence's partial sums are cut depends on its own length only
+                split_len = FP32_SPLIT_LEN
+                n_splits = max(1, -(-ctx.kv_len_bound // split_len))
+            else:
+                n_splits, split_len = plan_splits(ctx.n_rows, self.n_kv, ctx.kv_len_bound, rt.sm_count)
+            if n_splits > 1:
+                scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, self.dv, n_splits),),
+                                 torch.float32)
+        K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
+                    ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d, self.scale,
+                    self.window or 0, n_splits, split_len, scratch, rt.status, chunk=self.chunk or 0)
+        if self.gate:
+            gated = ws.get("cga_gated", (T, self.n_q * self.dv), x.dtype)
+            K.gate_mul(attn, proj, self.n_conv, gated)
+            attn = gated
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        return matmul(attn, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -17,12 +17,12 @@ class TokenEmbedding(Embedding):
     """resid[t] = table[token[t]], unscaled (engine/model.py:166,255 of
     davidjoyme/flashdecode-cuda), written as float32."""
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int):
-        self.name = f"{prefix}.weight"
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tensor: Optional[str] = None):
+        self.name = tensor or f"{prefix}.weight"        # ``tensor``: the table's full name where it is not <prefix>.weight
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size), "matrix")]
+        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size), "matrix", init="embedding")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt

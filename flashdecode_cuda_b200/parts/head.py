@@ -19,8 +19,9 @@ class LinearHead(Head):
     table to use when the checkpoint keeps no separate head
     (engine/loader.py:39-40)."""
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
-        self.name = f"{prefix}.weight"
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
+                 tensor: Optional[str] = None):
+        self.name = tensor or f"{prefix}.weight"        # ``tensor``: the matrix's full name where it is not <prefix>.weight
         self.vocab_size, self.hidden_size, self.tied_to = vocab_size, hidden_size, tied_to
 
     def tensor_specs(self) -> List[TensorSpec]:

@@ -1,0 +1,107 @@
+"""Routed feed-forward: a mixture of small experts chosen per token."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_part
+from ..weights.spec import TensorSpec
+from .base import FeedForward, Runtime
+from .linear import matmul
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """For the feed-forward's input h [T, hidden]:
+
+        s      = softmax(W_router h) over all ``n_experts + n_identity`` router outputs   (float32)
+        chosen = the ``top`` outputs with the largest s + correction
+        w      = s[chosen] / (sum of s[chosen] + 1e-20)
+        out    = sum over chosen e of w_e * expert_e(h)  +  shared(h)
+
+    An expert, and the shared expert, is down(act(up h)) with act = relu^2 and no biases.  The last
+    ``n_identity`` router outputs are identity experts: they have no tensors and pass h on.  ``shared_ff``
+    None: no shared expert.
+
+    All decisions are taken on the device (no read-back): the (token, choice) pairs are grouped by expert, each
+    group padded to whole row tiles, and two grouped products run over the tiles that exist.  Tensors:
+    ``<prefix>.e<i>.up`` [ff, hidden], ``<prefix>.e<i>.down`` [hidden, ff], ``<prefix>.router``,
+    ``<prefix>.correction``, ``<prefix>.shared.up`` / ``.down``.
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, n_experts: int, top: int, expert_ff: int, n_identity: int = 0,
+                 shared_ff: Optional[int] = None, correction: bool = True):
+        if n_experts < 0 or n_identity < 0 or not (1 <= top <= n_experts + n_identity) or expert_ff < 1:
+            raise ValueError(f"{prefix}: {top} choices among {n_experts} experts and {n_identity} identity experts")
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.E, self.n_identity, self.top, self.ff, self.shared_ff = n_experts, n_identity, top, expert_ff, shared_ff
+        self.has_correction = correction
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        specs = []
+        for e in range(self.E):
+            specs += [TensorSpec(f"{p}.e{e}.up", (self.ff, H), init="unit"),
+                      TensorSpec(f"{p}.e{e}.down", (H, self.ff), init="unit")]
+        specs.append(TensorSpec(f"{p}.router", (self.E + self.n_identity, H), init="unit"))
+        if self.has_correction:
+            specs.append(TensorSpec(f"{p}.correction", (self.E + self.n_identity,), "vector", init="bias"))
+        if self.shared_ff is not None:
+            specs += [TensorSpec(f"{p}.shared.up", (self.shared_ff, H), init="unit"),
+                      TensorSpec(f"{p}.shared.down", (H, self.shared_ff), init="unit")]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        if self.E:
+            self.w_up = torch.stack([tensors.pop(f"{p}.e{e}.up") for e in range(self.E)]).contiguous()       # [E, ff, H]
+            self.w_down = torch.stack([tensors.pop(f"{p}.e{e}.down") for e in range(self.E)]).contiguous()   # [E, H, ff]
+        else:
+            self.w_up = self.w_down = None
+        self.router = tensors[f"{p}.router"]
+        self.correction = tensors[f"{p}.correction"].float().contiguous() if self.has_correction else None
+        self.s_up = tensors.get(f"{p}.shared.up")
+        self.s_down = tensors.get(f"{p}.shared.down")
+
+    def weight_bytes(self) -> int:
+        """What a step reads at most: every expert once (a decode step of few tokens reads only the chosen ones)."""
+        n = self.router.numel() * self.router.element_size()
+        for w in (self.w_up, self.w_down, self.s_up, self.s_down):
+            if w is not None:
+                n += w.numel() * w.element_size()
+        return n
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.s_up if self.s_up is not None else self.router
+
+    def forward(self, ctx, x: torch.Tensor, parts_ok: bool = False) -> torch.Tensor:
+        T, ws, H, top = ctx.T, ctx.ws, self.hidden_size, self.top
+        ids = ws.get("moe_ids", (T, top), torch.int32)
+        wts = ws.get("moe_wts", (T, top), torch.float32)
+        K.moe_route(x, self.router, self.correction, ids, wts)
+        shared = None
+        if self.s_up is not None:
+            h = ws.get("moe_shared_h", (T, self.shared_ff), x.dtype)
+            matmul(x, self.s_up, None, h, status=self.rt.status)
+            K.relu2(h, h)
+            shared = ws.get("moe_shared_out", (T, H), x.dtype)
+            matmul(h, self.s_down, None, shared, target_ctas=4 * self.rt.sm_count, status=self.rt.status)
+        y = pair_pos = None
+        pair_pos = ws.get("moe_pair_pos", (T * top,), torch.int32)
+        if self.E:
+            cap = K.moe_grouped_rows(T * top, self.E)
+            sorted_pair = ws.get("moe_sorted", (cap,), torch.int32)
+            tile_expert = ws.get("moe_tile_expert", (cap // K.moe_tile_rows(),), torch.int32)
+            n_tiles = ws.get("moe_n_tiles", (1,), torch.int32)
+            K.moe_align(ids, self.E, pair_pos, sorted_pair, tile_expert, n_tiles)
+            act = ws.get("moe_act", (cap, self.ff), x.dtype)
+            K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top)
+            y = ws.get("moe_y", (cap, H), torch.float32)
+            K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top)
+        out = ws.get("ffn_out", (T, H), x.dtype)
+        K.moe_combine(y, x, shared, ids, wts, pair_pos, out, self.E)
+        return out

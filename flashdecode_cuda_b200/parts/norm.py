@@ -24,16 +24,23 @@ class RMSNorm(Norm):
 
     accepts_parts = True        # the kernel adds up to four float partial sums in order while it adds the residual
 
-    def __init__(self, prefix: str, size: int, eps: float):
-        self.name = f"{prefix}.weight"
-        self.size, self.eps = size, float(eps)
+    def __init__(self, prefix: str, size: int, eps: float, unit_offset: bool = False, tensor: Optional[str] = None,
+                 optional: bool = False):
+        """``unit_offset``: the stored weight lies around zero and the norm multiplies by 1 + weight (added in
+        float32 when the weights are bound).  ``tensor``: the weight's full name where it is not
+        ``<prefix>.weight``.  ``optional``: a checkpoint may lack the weight (a norm that never runs)."""
+        self.name = tensor or f"{prefix}.weight"
+        self.size, self.eps, self.unit_offset, self.optional = size, float(eps), bool(unit_offset), bool(optional)
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.name, (self.size,), "vector", init="norm")]
+        return [TensorSpec(self.name, (self.size,), "vector", optional=self.optional,
+                           init="norm_zero" if self.unit_offset else "norm")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
-        self.weight = tensors[self.name]
+        self.weight = tensors.get(self.name) if self.optional else tensors[self.name]
+        if self.unit_offset and self.weight is not None:
+            self.weight = (1.0 + self.weight.float()).contiguous()
 
     def forward(self, ctx, delta: Optional[torch.Tensor], resid: torch.Tensor, out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None, n_out: Optional[int] = None,

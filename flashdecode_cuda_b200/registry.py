@@ -6,8 +6,8 @@
   its one architecture (engine/model.py:74); here the model class is always
   chosen through this table.
 * ``PARTS``: (kind, name) -> the class that implements a part.  Kinds are
-  ``embedding``, ``position``, ``norm``, ``mixer``, ``feed_forward``, ``block``
-  and ``head``.  A blueprint names parts by (kind, name); nothing else in the
+  ``embedding``, ``position``, ``norm``, ``mixer``, ``feed_forward``, ``block``,
+  ``head`` and ``stream_op``.  A blueprint names parts by (kind, name); nothing else in the
   engine knows a part's class.
 
 A new architecture or part is added by calling ``register_architecture`` /
@@ -20,7 +20,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, Dict, Tuple, Type
 
-PART_KINDS = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head")
+PART_KINDS = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head", "stream_op")
 
 
 @dataclass(frozen=True)

@@ -101,7 +101,13 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu")
         t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
         if spec.init == "norm":
             t = 1.0 + 0.1 * t
-        elif spec.init in ("normal", "bias"):
+        elif spec.init == "norm_zero":
+            t = 0.1 * t
+        elif spec.init == "conv":
+            t = 0.5 * t
+        elif spec.init == "unit":
+            t = t / (spec.shape[-1] ** 0.5)
+        elif spec.init in ("normal", "bias", "embedding"):
             t = 0.02 * t
         else:
             raise ValueError(f"{spec.name}: unknown initialiser {spec.init!r}")

@@ -14,7 +14,9 @@ class TensorSpec:
     (norm weights, biases: a tensor stored in 32-bit stays so) or ``table``
     (integers: kept as int32).  ``optional``: absence is not an error.
     ``init``: how the random-weights mode draws it: ``normal`` N(0, 0.02),
-    ``norm`` 1 + N(0, 0.1), ``bias`` N(0, 0.02), ``zeros``."""
+    ``norm`` 1 + N(0, 0.1), ``norm_zero`` N(0, 0.1), ``conv`` N(0, 0.5), ``unit``
+    N(0, 1 / fan-in) (products that keep their input's scale), ``bias`` N(0, 0.02),
+    ``zeros``."""
 
     name: str
     shape: Tuple[int, ...]
