@@ -7,9 +7,12 @@
 //    grouped by expert, each group padded to whole row tiles, with the expert of
 //    every tile and the number of tiles;
 //  * moe_gemm: one CTA per (row tile, column tile): rows gathered through the
-//    grouping, the tile's expert's matrix, k ascending in one fmaf chain per
-//    output (no bit depends on what else is in the step); epilogue relu^2 into
-//    the grouped activations, or float rows for the combine;
+//    grouping, the tile's expert's matrix; epilogue relu^2 into the grouped
+//    activations, or float rows for the combine.  float32: CUDA cores, k ascending
+//    in one fmaf chain per output (no bit depends on what else is in the step);
+//    bfloat16: tensor cores (mma.m16n8k16, float accumulators, cp.async ring of
+//    three 64-deep k-blocks, swizzled tiles), row tiles of 32 for steps of few
+//    tokens and of 128 for prompts;
 //  * moe_combine: per token, sum over its choices of weight * (expert row, or the
 //    token's own input for an identity expert), plus the shared expert's row.
 //
@@ -17,7 +20,7 @@
 // pass their input on.
 #include <math.h>
 
-#include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace fd {
 
@@ -92,7 +95,7 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* 
 // and n_tiles.
 __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ pair_pos,
                                  int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ n_tiles,
-                                 int cap) {
+                                 int cap, int MT) {
     extern __shared__ int a_s[];           // [E] counts, [E] offsets, [E] fill
     int* cnt = a_s;
     int* off = a_s + E;
@@ -109,12 +112,12 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int*
         int run = 0;
         for (int e = 0; e < E; ++e) {
             off[e] = run;
-            const int tiles = (cnt[e] + MOE_MT - 1) / MOE_MT;
-            for (int i = 0; i < tiles; ++i) tile_expert[run / MOE_MT + i] = e;
-            run += tiles * MOE_MT;
+            const int tiles = (cnt[e] + MT - 1) / MT;
+            for (int i = 0; i < tiles; ++i) tile_expert[run / MT + i] = e;
+            run += tiles * MT;
         }
         total_s = run;
-        *n_tiles = run / MOE_MT;
+        *n_tiles = run / MT;
     }
     __syncthreads();
     const int total = min(total_s, cap);
@@ -196,6 +199,133 @@ moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restri
     }
 }
 
+
+// The same product on the tensor cores for bfloat16 (K a multiple of 8).  A CTA of WM x WN warps takes BM grouped rows
+// and BN columns; a warp a (BM / WM) x (BN / WN) part of it.
+template <int BM, int BN, int WM, int WN, int MODE>
+__global__ void __launch_bounds__(WM * WN * 32)
+moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
+                    const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
+                    const int* __restrict__ n_tiles, int top, int N, int K) {
+    constexpr int THREADS = WM * WN * 32, BK = 64, STAGES = 3;
+    constexpr int TM = BM / WM, TN = BN / WN, MI = TM / 16, NI = TN / 8;
+    static_assert(TM % 16 == 0 && TN % 16 == 0, "a warp takes whole 16 x 16 parts");
+    const int tile = blockIdx.y;
+    if (tile >= *n_tiles) return;
+    extern __shared__ __align__(128) unsigned char mm_smem[];
+    unsigned char* a_s = mm_smem;                                   // [STAGES][BM][64] bf16, swizzled
+    unsigned char* b_s = a_s + STAGES * BM * BK * 2;                // [STAGES][BN][64]
+    int* row_s = reinterpret_cast<int*>(b_s + STAGES * BN * BK * 2);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp / WN, wn = warp % WN;
+    const int n0 = blockIdx.x * BN;
+    for (int i = tid; i < BM; i += THREADS) {
+        const int pr = sorted_pair[tile * BM + i];
+        row_s[i] = pr < 0 ? -1 : (MODE == 0 ? pr / top : tile * BM + i);
+    }
+    __syncthreads();
+    const __nv_bfloat16* we = w + (size_t)tile_expert[tile] * N * K;
+    const int nkb = (K + BK - 1) / BK;
+    auto issue = [&](int kb, int stage) {
+        unsigned char* as = a_s + stage * BM * BK * 2;
+        unsigned char* bs = b_s + stage * BN * BK * 2;
+        for (int c = tid; c < BM * 8; c += THREADS) {
+            const int r = c >> 3, cc = c & 7;
+            const int k = kb * BK + cc * 8;
+            const int src = row_s[r];
+            const bool ok = src >= 0 && k < K;
+            cp_async16(smem_u32(as + swz<BK>(r, cc)), ok ? a + (size_t)src * K + k : a, ok ? 16 : 0);
+        }
+        for (int c = tid; c < BN * 8; c += THREADS) {
+            const int r = c >> 3, cc = c & 7;
+            const int k = kb * BK + cc * 8;
+            const bool ok = n0 + r < N && k < K;
+            cp_async16(smem_u32(bs + swz<BK>(r, cc)), ok ? we + (size_t)(n0 + r) * K + k : we, ok ? 16 : 0);
+        }
+    };
+    float acc[MI][NI][4];
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < NI; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < nkb) issue(s, s);
+        cp_async_commit();
+    }
+    const int mi8 = lane >> 3;
+    for (int kb = 0; kb < nkb; ++kb) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();              // block kb has landed for everyone, and everyone is done with block kb - 1
+        if (kb + STAGES - 1 < nkb) issue(kb + STAGES - 1, (kb + STAGES - 1) % STAGES);
+        cp_async_commit();
+        const unsigned char* as = a_s + (kb % STAGES) * BM * BK * 2;
+        const unsigned char* bs = b_s + (kb % STAGES) * BN * BK * 2;
+#pragma unroll
+        for (int ks = 0; ks < BK / 16; ++ks) {
+            uint32_t af[MI][4];
+#pragma unroll
+            for (int i = 0; i < MI; ++i) {
+                const int r = wm * TM + i * 16 + (mi8 & 1) * 8 + (lane & 7);
+                ldmatrix_x4(smem_u32(as + swz<BK>(r, ks * 2 + (mi8 >> 1))), af[i][0], af[i][1], af[i][2], af[i][3]);
+            }
+#pragma unroll
+            for (int jp = 0; jp < NI / 2; ++jp) {
+                const int r = wn * TN + jp * 16 + (mi8 >> 1) * 8 + (lane & 7);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(smem_u32(bs + swz<BK>(r, ks * 2 + (mi8 & 1))), b0, b1, b2, b3);
+#pragma unroll
+                for (int i = 0; i < MI; ++i) {
+                    mma_bf16(acc[i][2 * jp], af[i][0], af[i][1], af[i][2], af[i][3], b0, b1);
+                    mma_bf16(acc[i][2 * jp + 1], af[i][0], af[i][1], af[i][2], af[i][3], b2, b3);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int r = wm * TM + i * 16 + (lane >> 2) + hh * 8;
+            if (row_s[r] < 0) continue;
+            const size_t orow = (size_t)(tile * BM + r) * N;
+#pragma unroll
+            for (int j = 0; j < NI; ++j) {
+                const int c = n0 + wn * TN + j * 8 + (lane & 3) * 2;
+                float v0 = acc[i][j][hh * 2], v1 = acc[i][j][hh * 2 + 1];
+                if (MODE == 0) {
+                    v0 = fmaxf(v0, 0.f); v0 *= v0;
+                    v1 = fmaxf(v1, 0.f); v1 *= v1;
+                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out) + orow + c;
+                    if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v0, v1);
+                    else { if (c < N) o[0] = __float2bfloat16_rn(v0); if (c + 1 < N) o[1] = __float2bfloat16_rn(v1); }
+                } else {
+                    float* o = static_cast<float*>(out) + orow + c;
+                    if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
+                    else { if (c < N) o[0] = v0; if (c + 1 < N) o[1] = v1; }
+                }
+            }
+        }
+}
+
+template <int BM, int BN, int WM, int WN, int MODE>
+static int launch_moe_mma(const void* a, const void* w, void* out, const int* sorted_pair, const int* tile_expert,
+                          const int* n_tiles, int cap, int top, int N, int K, cudaStream_t stream) {
+    auto k = moe_gemm_mma_kernel<BM, BN, WM, WN, MODE>;
+    const size_t smem = (size_t)3 * (BM + BN) * 64 * 2 + BM * sizeof(int);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(-3, "moe_gemm: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, cap / BM);
+    FD_REQUIRE(grid.y <= 65535, -2, "moe_gemm: %d row tiles are too many", (int)grid.y);
+    return launch("moe_gemm", k, grid, dim3(WM * WN * 32), smem, stream, dim3(1, 1, 1), (const __nv_bfloat16*)a,
+                  (const __nv_bfloat16*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K);
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ x, const T* __restrict__ shared,
                                    const int* __restrict__ ids, const float* __restrict__ wts,
@@ -223,7 +353,9 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
 using namespace fd;
 typedef __nv_bfloat16 bf16;
 
-extern "C" int fd_moe_tile_rows() { return MOE_MT; }
+// Rows of a tile of the grouped products: 32 on the CUDA cores (float32) and for steps of few tokens, 128 for
+// bfloat16 steps with many rows per expert.
+extern "C" int fd_moe_tile_rows(int dtype, int rows_per_expert) { return dtype == 1 && rows_per_expert >= 96 ? 128 : MOE_MT; }
 
 // x [T, H] and w [n_out, H] of type dtype (0 float32, 1 bfloat16); correction [n_out] float or null;
 // ids [T, top] int32 and wts [T, top] float come back.
@@ -241,23 +373,37 @@ extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float
 }
 
 // cap: rows of the grouped buffers, at least P rounded up to whole tiles plus one tile per expert.
+// mt: rows of a tile (32 or 128).
 extern "C" int fd_moe_align(const int* ids, int P, int E, int* pair_pos, int* sorted_pair, int* tile_expert,
-                            int* n_tiles, int cap, cudaStream_t stream) {
+                            int* n_tiles, int cap, int mt, cudaStream_t stream) {
     FD_REQUIRE(E >= 1 && E <= 4096, -2, "moe_align: %d experts (1..4096)", E);
-    const long long worst = (long long)P + (long long)(E < P ? E : P) * (MOE_MT - 1);     // every group's last tile nearly empty
-    FD_REQUIRE(cap % MOE_MT == 0 && (long long)cap >= (worst + MOE_MT - 1) / MOE_MT * MOE_MT, -2,
+    FD_REQUIRE(mt == 32 || mt == 128, -2, "moe_align: tiles of %d rows (32 or 128)", mt);
+    const long long worst = (long long)P + (long long)(E < P ? E : P) * (mt - 1);     // every group's last tile nearly empty
+    FD_REQUIRE(cap % mt == 0 && (long long)cap >= (worst + mt - 1) / mt * mt, -2,
                "moe_align: %d grouped rows cannot hold %d pairs of %d experts", cap, P, E);
     return launch("moe_align", moe_align_kernel, dim3(1), dim3(1024), 3 * (size_t)E * sizeof(int), stream, dim3(1, 1, 1),
-                  ids, P, E, pair_pos, sorted_pair, tile_expert, n_tiles, cap);
+                  ids, P, E, pair_pos, sorted_pair, tile_expert, n_tiles, cap, mt);
 }
 
 // mode 0: a = x [T, K], out = act [cap, N] (dtype) = relu(x W_e^T)^2;  mode 1: a = act [cap, K], out = y [cap, N] float.
 // w [E, N, K].
+// mt: the tile rows the grouping was made with.
 extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, int mode, const int* sorted_pair,
-                           const int* tile_expert, const int* n_tiles, int cap, int top, int N, int K,
+                           const int* tile_expert, const int* n_tiles, int cap, int mt, int top, int N, int K,
                            cudaStream_t stream) {
     if (cap == 0) return 0;
-    FD_REQUIRE(cap % MOE_MT == 0 && N > 0 && K > 0, -2, "moe_gemm: bad sizes");
+    FD_REQUIRE(cap % mt == 0 && N > 0 && K > 0, -2, "moe_gemm: bad sizes");
+    if (dtype == 1 && K % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0) {
+        if (mt == 128) {
+            if (mode == 0) return launch_moe_mma<128, 128, 2, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+            return launch_moe_mma<128, 128, 2, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+        }
+        if (mt == 32) {
+            if (mode == 0) return launch_moe_mma<32, 64, 1, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+            return launch_moe_mma<32, 64, 1, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+        }
+    }
+    FD_REQUIRE(mt == MOE_MT, -2, "moe_gemm: the CUDA-core product takes tiles of %d rows, not %d", MOE_MT, mt);
     dim3 grid((N + MOE_NT - 1) / MOE_NT, cap / MOE_MT);
     FD_REQUIRE(grid.y <= 65535, -2, "moe_gemm: %d row tiles are too many", (int)grid.y);
 #define FD_MG(T_, M_)                                                                                                \

@@ -100,10 +100,10 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gate_mul": [P, P, I, P, I, I, I, P],
         "fd_add_concat": [P, I, P, P, P, I, I, I, P],
         "fd_relu2": [P, P, I, LL, P],
-        "fd_moe_tile_rows": [],
+        "fd_moe_tile_rows": [I, I],
         "fd_moe_route": [P, P, I, P, P, P, I, I, I, I, P],
-        "fd_moe_align": [P, I, I, P, P, P, P, I, P],
-        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, P],
+        "fd_moe_align": [P, I, I, P, P, P, P, I, I, P],
+        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, P],
         "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
@@ -612,14 +612,18 @@ def relu2(x: torch.Tensor, out: torch.Tensor) -> None:
     _check(lib().fd_relu2(_ptr(x), _ptr(out), _dt(x.dtype), x.numel(), _stream()))
 
 
-def moe_tile_rows() -> int:
-    return int(lib().fd_moe_tile_rows())
+def moe_tile_rows(dtype: torch.dtype = torch.float32, n_pairs: int = 0, n_experts: int = 1, k_sizes=()) -> int:
+    """Rows of a tile of the grouped products: 32, or 128 for bfloat16 steps with many (token, choice) pairs per
+    expert (prompts).  ``k_sizes``: the inner sizes of the products; one that is no multiple of 8 keeps the products
+    on the CUDA cores, whose tiles have 32 rows."""
+    if dtype != torch.bfloat16 or any(k % 8 for k in k_sizes):
+        return int(lib().fd_moe_tile_rows(0, 0))
+    return int(lib().fd_moe_tile_rows(1, n_pairs // max(1, n_experts)))
 
 
-def moe_grouped_rows(n_pairs: int, n_experts: int) -> int:
+def moe_grouped_rows(n_pairs: int, n_experts: int, mt: int) -> int:
     """Rows of the grouped buffers that hold ``n_pairs`` (token, choice) pairs of ``n_experts`` experts whatever the
-    routing: every expert's group is padded to whole tiles."""
-    mt = moe_tile_rows()
+    routing: every expert's group is padded to whole tiles of ``mt`` rows."""
     worst = n_pairs + min(n_experts, n_pairs) * (mt - 1)
     return -(-worst // mt) * mt
 
@@ -639,27 +643,29 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
 
 
 def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_pair: torch.Tensor,
-              tile_expert: torch.Tensor, n_tiles: torch.Tensor) -> None:
-    """Group the (token, choice) pairs of ``ids`` by expert (outputs >= ``n_experts`` are left out: pair_pos -1)."""
+              tile_expert: torch.Tensor, n_tiles: torch.Tensor, mt: int) -> None:
+    """Group the (token, choice) pairs of ``ids`` by expert, every group padded to whole tiles of ``mt`` rows
+    (outputs >= ``n_experts`` are left out: pair_pos -1)."""
     P = ids.numel()
     cap = sorted_pair.numel()
     assert all(t.dtype == torch.int32 for t in (ids, pair_pos, sorted_pair, tile_expert, n_tiles))
-    assert pair_pos.numel() >= P and tile_expert.numel() * moe_tile_rows() >= cap
+    assert pair_pos.numel() >= P and tile_expert.numel() * mt >= cap
     _check(lib().fd_moe_align(_ptr(ids), P, n_experts, _ptr(pair_pos), _ptr(sorted_pair), _ptr(tile_expert),
-                              _ptr(n_tiles), cap, _stream()))
+                              _ptr(n_tiles), cap, mt, _stream()))
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, sorted_pair: torch.Tensor,
-             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int) -> None:
+             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int) -> None:
     """Grouped product with the experts' stacked matrices w [E, N, K].  ``down`` False: a = x [T, K] (rows gathered
     through the grouping), out [cap, N] = relu(x w_e^T)^2 in a's dtype; True: a = the grouped activations [cap, K],
-    out [cap, N] float32."""
+    out [cap, N] float32.  ``mt``: the tile rows the grouping was made with.  bfloat16 with K a multiple of 8 runs on
+    the tensor cores, everything else on the CUDA cores (tiles of 32 rows only)."""
     E, N, Kd = w.shape
     cap = sorted_pair.numel()
     assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N)
     assert out.dtype == (torch.float32 if down else a.dtype) and (not down or a.shape[0] == cap)
     _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), int(down), _ptr(sorted_pair), _ptr(tile_expert),
-                             _ptr(n_tiles), cap, top, N, Kd, _stream()))
+                             _ptr(n_tiles), cap, mt, top, N, Kd, _stream()))
 
 
 def moe_combine(y: Optional[torch.Tensor], x: torch.Tensor, shared: Optional[torch.Tensor], ids: torch.Tensor,

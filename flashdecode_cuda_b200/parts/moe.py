@@ -93,15 +93,16 @@ class RoutedExperts(FeedForward):
         y = pair_pos = None
         pair_pos = ws.get("moe_pair_pos", (T * top,), torch.int32)
         if self.E:
-            cap = K.moe_grouped_rows(T * top, self.E)
+            mt = K.moe_tile_rows(x.dtype, T * top, self.E, (H, self.ff))
+            cap = K.moe_grouped_rows(T * top, self.E, mt)
             sorted_pair = ws.get("moe_sorted", (cap,), torch.int32)
-            tile_expert = ws.get("moe_tile_expert", (cap // K.moe_tile_rows(),), torch.int32)
+            tile_expert = ws.get("moe_tile_expert", (cap // mt,), torch.int32)
             n_tiles = ws.get("moe_n_tiles", (1,), torch.int32)
-            K.moe_align(ids, self.E, pair_pos, sorted_pair, tile_expert, n_tiles)
+            K.moe_align(ids, self.E, pair_pos, sorted_pair, tile_expert, n_tiles, mt)
             act = ws.get("moe_act", (cap, self.ff), x.dtype)
-            K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top)
+            K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
             y = ws.get("moe_y", (cap, H), torch.float32)
-            K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top)
+            K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top, mt)
         out = ws.get("ffn_out", (T, H), x.dtype)
         K.moe_combine(y, x, shared, ids, wts, pair_pos, out, self.E)
         return out

@@ -24,6 +24,8 @@ class RotaryHalf(Position):
     # Tables longer than this many positions are built for what the first cache asks for instead of the
     # configuration's whole max_position_embeddings (8 bytes per position and pair of dims).
     FULL_TABLE_LIMIT = 1 << 18
+    # ... but for at least this many, so that a configuration without a limit of its own serves later, longer caches
+    MIN_TABLE = 1 << 16
 
     def __init__(self, head_dim: int, theta: float, max_positions: int):
         self.head_dim, self.theta, self.max_positions = head_dim, float(theta), max_positions
@@ -43,6 +45,8 @@ class RotaryHalf(Position):
             return
         if self.max_positions <= self.FULL_TABLE_LIMIT:
             n = self.max_positions
+        else:
+            n = max(n, self.MIN_TABLE)
         d = self.head_dim
         inv_freq = 1.0 / (self.theta ** (torch.arange(0, d, 2).float() / d))
         freqs = torch.outer(torch.arange(n).float(), inv_freq)
