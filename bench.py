@@ -28,6 +28,12 @@ above 15 % (testing/phase1.py:425-434).  The cache block is 16 tokens, as the
 benchmark configuration says; the library's own default of 64 is measured
 beside it (``points.decode_b8_block64``, ``points.prefill_block64_ms``).
 
+``--compare lonasun`` leaves all of that aside and measures the Lonasun design beside the Qwen2 dense decoder of the
+same width, heads, layer runs and feed-forward work per token (random weights, a window as long as Lonasun's chunk):
+prefill and decode throughput of both at a few layer sizes, and for every mixer and feed-forward the device time of
+its kernels against the least time its operations and bytes need at the measured peaks.  It prints one JSON line of
+its own.
+
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from
 the stated fallback.  Only one GPU is used: for --gpus > 1 it says so and exits
 with 2.
@@ -275,6 +281,164 @@ def prefill_flops(cfg, tokens: int) -> float:
 # ---------------------------------------------------------------------------
 # the reference arm: davidjoyme/flashdecode-cuda itself, from its source tree
 
+# ---------------------------------------------------------------------------
+# --compare lonasun: the design beside the closest dense model at equal sizes
+
+COMPARE_SIZES = {
+    # width, heads, kv heads, head size, experts, identity experts, choices, expert ff, shared ff, taps, rotated, chunk
+    "w1024": dict(width=1024, heads=8, kv=2, dim=128, experts=16, identity=2, top=4, ff=512, shared=1024, taps=4, rot=64,
+                  chunk=1024),
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, experts=32, identity=4, top=6, ff=768, shared=1536, taps=4, rot=64,
+                  chunk=1024),
+    "w2048-d64": dict(width=2048, heads=32, kv=8, dim=64, experts=64, identity=0, top=8, ff=512, shared=2048, taps=3,
+                      rot=32, chunk=512),
+}
+COMPARE_VOCAB = 32768
+
+
+def compare_configs(sz: dict):
+    """(Lonasun config dictionary, Qwen2 config dictionary) of equal width, heads and layer runs: six Lonasun layers of
+    which three run twice (nine runs) beside nine dense layers whose feed-forward does the operations per token that
+    Lonasun's chosen experts and shared expert do (three matrices of the dense one against two of each expert)."""
+    mixer = {"conv": sz["taps"], "dim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv"], "mask": {"size": sz["chunk"]},
+             "rot": {"base": 1000000.0, "dims": sz["rot"]}, "scale": sz["dim"] ** -0.5, "vdim": sz["dim"]}
+    mlp = {"expert": {"ff": sz["ff"]}, "kind": "moe",
+           "router": {"experts": sz["experts"], "identity": sz["identity"], "top": sz["top"]}, "shared": {"ff": sz["shared"]}}
+    lona = {"architecture": "Lonasun", "vocab": COMPARE_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(6)],
+            "loop": {"start": 1, "stop": 4, "times": 2}}
+    real_share = sz["experts"] / (sz["experts"] + sz["identity"])
+    inter = int(round((sz["top"] * real_share * sz["ff"] + sz["shared"]) * 2 / 3 / 64)) * 64
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "hidden_size": sz["width"],
+            "intermediate_size": inter, "num_hidden_layers": 9, "num_attention_heads": sz["heads"],
+            "num_key_value_heads": sz["kv"], "head_dim": sz["dim"], "vocab_size": COMPARE_VOCAB, "rms_norm_eps": 1e-5,
+            "rope_theta": 1000000.0, "max_position_embeddings": 8192, "tie_word_embeddings": False,
+            "use_sliding_window": True, "sliding_window": sz["chunk"], "max_window_layers": 0, "attention_bias": False}
+    return lona, qwen
+
+
+def compare_one(cfgd: dict, pk: dict, batch: int, context: int, prompt: int, steps: int, warmup: int, seed: int) -> dict:
+    import torch
+    from flashdecode_cuda_b200.config import config_from_dict
+    from flashdecode_cuda_b200.engine import Engine, Model, random_weights
+    from flashdecode_cuda_b200.measure import PartTimer, part_work, routing_of
+    cfg = config_from_dict(cfgd)
+    model = Model.from_config(cfg, torch.bfloat16, "cuda")
+    model.bind(random_weights(model, seed, torch.bfloat16, device="cuda", qkv_bias=False))
+    engine = Engine(model)
+    tflops, gbs = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    out = {}
+
+    def parts_of(ctx_lens, q_lens, n_steps):
+        """Per kind of part: device time of its kernels over one step, the time its work needs at the peaks."""
+        with PartTimer(model) as timer:
+            times = timer_steps(timer, n_steps)
+        T = sum(q_lens)
+        need = {"mixer": 0.0, "feed_forward": 0.0}
+        for run in model.schedule:
+            b = model.blocks[run.layer]
+            fl, by = part_work(b.mixer, ctx_lens, q_lens)
+            need["mixer"] += max(fl / tflops, by / gbs) * 1e3
+            ff = b.feed_forward
+            if type(ff).__name__ == "RoutedExperts":
+                share, touched = routing_of(model, T, ff.top, ff.E)
+                fl, by = part_work(ff, ctx_lens, q_lens, share, touched)
+            else:
+                fl, by = part_work(ff, ctx_lens, q_lens)
+            need["feed_forward"] += max(fl / tflops, by / gbs) * 1e3
+        res = {}
+        for label, kernels in times.items():
+            ms = sum(v[0] for v in kernels.values())
+            res[label] = {"ms": round(ms, 4), "kernels": {k: [round(v[0], 4), v[1]] for k, v in sorted(kernels.items())}}
+            if label in need:
+                res[label]["roofline_ms"] = round(need[label], 4)
+                res[label]["frac"] = round(need[label] / ms, 4)
+        return res
+
+    # prefill: one prompt in one step
+    cache = model.new_cache(batch_size=1, max_len=prompt, block_size=LIB_BLOCK_SIZE)
+    (p,) = ragged_prompts(1, prompt, prompt, model.vocab_size, seed)
+
+    def prefill_once():
+        slot = cache.admit()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        model.step(cache, [slot], [p], "last")
+        b.record()
+        torch.cuda.synchronize()
+        cache.release(slot)
+        return a.elapsed_time(b)
+    ms = min([prefill_once() for _ in range(warmup + TRIALS)][warmup:])
+    out["prefill"] = {"tokens": prompt, "ms": round(ms, 3), "tok_s": round(prompt / ms * 1e3, 1)}
+
+    def timer_steps(timer, n):
+        agg = None
+        for i in range(n + 1):
+            prefill_once() if mode[0] == "prefill" else decode_once()
+            got = timer.collect()
+            if i == 0:
+                continue                                   # the first instrumented step warms the wrappers up
+            if agg is None:
+                agg = got
+            else:                                          # the fastest of the steps, kernel by kernel
+                for lab, d in got.items():
+                    for k, v in d.items():
+                        if v[0] < agg[lab][k][0]:
+                            agg[lab][k] = v
+        return agg
+    mode = ["prefill"]
+    out["prefill"]["parts"] = parts_of([0], [prompt], 3)
+    del cache
+
+    # decode: ragged prompts, then one token each from captured graphs; the parts from eager steps at the same lengths
+    r = decode_run(engine, batch, context, steps, warmup, seed, e2e=False, prompt_range=(context // 2, context * 3 // 4),
+                   block_size=LIB_BLOCK_SIZE, trials=3)
+    out["decode"] = {"batch": batch, "mean_context": round(r["mean_context"], 1), "ms_per_step": round(r["ms_per_step"], 4),
+                     "tok_s": round(r["tok_s"], 1), "launches_per_step": r["launches_per_step"]}
+    del r["decoder"]
+    cache = model.new_cache(batch_size=batch, max_len=context, block_size=LIB_BLOCK_SIZE)
+    prompts = ragged_prompts(batch, context // 2, context * 3 // 4, model.vocab_size, seed)
+    slots = [cache.admit() for _ in prompts]
+    model.step(cache, slots, prompts, "last")
+
+    def decode_once():
+        model.step(cache, slots, [[1]] * batch, "last")
+    for _ in range(3):
+        decode_once()
+    mode[0] = "decode"
+    lens = [cache.length(s) + 2 for s in slots]            # the lengths at the middle of the instrumented steps
+    out["decode"]["parts"] = parts_of(lens, [1] * batch, 4)
+    model.check_status()
+    return out
+
+
+def compare_main(args) -> int:
+    import torch
+    pk = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    sizes = {}
+    for name in (args.compare_sizes.split(",") if args.compare_sizes else COMPARE_SIZES):
+        lona, qwen = compare_configs(COMPARE_SIZES[name])
+        entry = {"sizes": COMPARE_SIZES[name], "dense_intermediate": qwen["intermediate_size"]}
+        for key, cfgd in (("lonasun", lona), ("qwen2", qwen)):
+            entry[key] = compare_one(cfgd, pk, args.batch, 2048, 2048, min(args.steps, 64), max(3, args.warmup), args.seed)
+            torch.cuda.empty_cache()
+        entry["ratios"] = {
+            "prefill_tok_s": round(entry["lonasun"]["prefill"]["tok_s"] / entry["qwen2"]["prefill"]["tok_s"], 3),
+            "decode_tok_s": round(entry["lonasun"]["decode"]["tok_s"] / entry["qwen2"]["decode"]["tok_s"], 3)}
+        for phase in ("prefill", "decode"):
+            for part in ("mixer", "feed_forward"):
+                a, b = entry["lonasun"][phase]["parts"][part], entry["qwen2"][phase]["parts"][part]
+                entry["ratios"][f"{phase}_{part}_frac"] = [a["frac"], b["frac"], round(a["frac"] / b["frac"], 3)]
+        sizes[name] = entry
+    print(json.dumps({"compare": "lonasun", "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic: random weights",
+                      "peaks": pk, "batch": args.batch, "prompt": 2048, "context": 2048, "block_size": LIB_BLOCK_SIZE,
+                      "clocks": clocks.stop(), "sizes": sizes}))
+    return 0
+
+
 def find_reference():
     """(path, places tried): the first folder that holds the reference's engine/model.py and config.py."""
     tried = [ROOT / "baseline" / "_ref"]
@@ -485,6 +649,9 @@ def main() -> int:
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 point (slow at the larger presets)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the main run through the true 32-bit path (with --no-points)")
+    ap.add_argument("--compare", default="", choices=["", "lonasun"],
+                    help="measure this design beside the closest dense model at equal sizes instead of the default run")
+    ap.add_argument("--compare-sizes", default="", help="with --compare: names of the sizes to run, with commas (default: all)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: only for --impl reference, to try that arm on a machine without a GPU (float32)")
     args = ap.parse_args()
@@ -494,6 +661,8 @@ def main() -> int:
         return 2
     if args.impl == "reference":
         return reference_main(args)
+    if args.compare:
+        return compare_main(args)
     warmup = max(3, args.warmup)
 
     import torch

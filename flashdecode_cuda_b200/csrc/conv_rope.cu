@@ -23,6 +23,12 @@
 
 namespace fd {
 
+constexpr int CONV_MAX_TAPS = 8;      // more taps than this take the loop that loads one value at a time
+
+// A CTA takes one head (of q, k or v) of one token; a thread one channel of it: it loads the values its taps see
+// (independent loads, issued together), convolves, leaves the result in shared memory for its rotation partner, rotates
+// and stores.  In a step of single tokens the same thread also moves the channel's state on: it holds the old state in
+// registers already.
 template <typename T>
 __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
                                         float* __restrict__ state, T* __restrict__ q_out,
@@ -34,73 +40,90 @@ __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, cons
                                         const int* __restrict__ block_table, int max_blocks, int num_blocks,
                                         int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
                                         int update_state, int* status) {
-    extern __shared__ float y_s[];                 // the token's convolved channels [C]
-    const int t = blockIdx.x;
+    extern __shared__ float y_s[];                 // the head's convolved channels
+    const int t = blockIdx.x, hu = blockIdx.y;     // head unit: q heads, then k heads, then v heads
     const int r = tok_row[t];
     const int slot = row_slot[r];
     if (slot < 0) return;                          // padding row
     const int C = (n_q + n_kv) * d + n_kv * dv;
+    const bool is_v = hu >= n_q + n_kv;
+    const int width = is_v ? dv : d;
+    const int c0 = is_v ? (n_q + n_kv) * d + (hu - n_q - n_kv) * dv : hu * d;     // the head's first channel
+    const int j = threadIdx.x;
     const int q_start = row_q_start[r];
     const int i = t - q_start;                     // index of the token among the row's new tokens
     const int pos = tok_pos[t];
     const int hist = taps - 1;
-    const float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
+    float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
+    const bool move_state = update_state && st != nullptr && row_q_len[r] == 1;
 
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.f;
-        for (int k = 0; k < taps; ++k) {
-            const int m = i - hist + k;            // index among the row's new tokens of the value this tap sees
-            const float u = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
-                                   : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
-            acc = fmaf(conv_w[(size_t)c * taps + k], u, acc);
+    float y = 0.f;
+    if (j < width) {
+        const int c = c0 + j;
+        if (taps <= CONV_MAX_TAPS) {
+            float u[CONV_MAX_TAPS], wk[CONV_MAX_TAPS];
+#pragma unroll
+            for (int k = 0; k < CONV_MAX_TAPS; ++k) {
+                u[k] = 0.f; wk[k] = 0.f;
+                if (k < taps) {
+                    const int m = i - hist + k;    // index among the row's new tokens of the value this tap sees
+                    wk[k] = conv_w[(size_t)c * taps + k];
+                    u[k] = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
+                                  : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < CONV_MAX_TAPS; ++k)
+                if (k < taps) y = fmaf(wk[k], u[k], y);
+            if (move_state) {                      // i == 0: u[0 .. hist-1] is the old state, u[hist] this token's value
+#pragma unroll
+                for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
+                    if (k < hist) st[(size_t)k * C + c] = u[k + 1];
+            }
+        } else {
+            for (int k = 0; k < taps; ++k) {
+                const int m = i - hist + k;
+                const float u = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
+                                       : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
+                y = fmaf(conv_w[(size_t)c * taps + k], u, y);
+            }
+            if (move_state) {
+                for (int s = 0; s + 1 < hist; ++s) st[(size_t)s * C + c] = st[(size_t)(s + 1) * C + c];
+                st[(size_t)(hist - 1) * C + c] = to_float(proj[(size_t)t * ld + c]);
+            }
         }
-        y_s[c] = acc;
+        y_s[j] = y;
     }
     __syncthreads();
-    // a step of single tokens: this CTA is the only reader of the row's state, so it may move it on
-    if (update_state && state != nullptr && row_q_len[r] == 1) {
-        float* sw = state + (size_t)slot * hist * C;
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
-            for (int s = 0; s + 1 < hist; ++s) sw[(size_t)s * C + c] = sw[(size_t)(s + 1) * C + c];
-            sw[(size_t)(hist - 1) * C + c] = to_float(proj[(size_t)t * ld + c]);
-        }
-    }
+    if (j >= width) return;
 
     const int half = rot >> 1;
-    bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
-    if (!pos_ok && threadIdx.x == 0) set_status(status, STATUS_BAD_POSITION);
-    const float* cs = cos_t + (size_t)(pos_ok ? pos : 0) * half;
-    const float* sn = sin_t + (size_t)(pos_ok ? pos : 0) * half;
-
-    T* kdst = nullptr;
-    T* vdst = nullptr;
-    if (write_kv && pos >= 0) {
-        const int col = pos / block_size;
-        const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
-        if (blk < 0 || blk >= num_blocks) {
-            if (threadIdx.x == 0) set_status(status, STATUS_BAD_BLOCK);
-        } else {
-            kdst = k_pool + ((size_t)blk * n_kv * block_size + (pos % block_size)) * d;
-            vdst = v_pool + ((size_t)blk * n_kv * block_size + (pos % block_size)) * dv;
-        }
+    const bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
+    if (!pos_ok && j == 0 && hu == 0) set_status(status, STATUS_BAD_POSITION);
+    if (!is_v && j < rot && pos_ok) {              // q and k heads: rotate the leading `rot` dimensions
+        const float* cs = cos_t + (size_t)pos * half;
+        const float* sn = sin_t + (size_t)pos * half;
+        if (j < half) y = y * cs[j] - y_s[j + half] * sn[j];
+        else y = y * cs[j - half] + y_s[j - half] * sn[j - half];
     }
-    // q and k heads: rotate the leading `rot` dimensions, pass the others on
-    const int n_qk = (n_q + n_kv) * d;
-    for (int e = threadIdx.x; e < n_qk; e += blockDim.x) {
-        const int h = e / d, j = e - h * d;
-        float y = y_s[e];
-        if (j < rot && pos_ok) {
-            if (j < half) y = y * cs[j] - y_s[e + half] * sn[j];
-            else y = y * cs[j - half] + y_s[e - half] * sn[j - half];
-        }
-        if (h < n_q) q_out[(size_t)t * n_q * d + e] = from_float<T>(y);
-        else if (kdst != nullptr) kdst[(size_t)(h - n_q) * block_size * d + j] = from_float<T>(y);
+    if (hu < n_q) {
+        q_out[(size_t)t * n_q * d + c0 + j] = from_float<T>(y);
+        return;
     }
-    if (vdst != nullptr)
-        for (int e = threadIdx.x; e < n_kv * dv; e += blockDim.x) {
-            const int h = e / dv, j = e - h * dv;
-            vdst[(size_t)h * block_size * dv + j] = from_float<T>(y_s[n_qk + e]);
-        }
+    if (!write_kv || pos < 0) return;
+    const int col = pos / block_size;
+    const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
+    if (blk < 0 || blk >= num_blocks) {
+        if (j == 0) set_status(status, STATUS_BAD_BLOCK);
+        return;
+    }
+    if (is_v) {
+        const int h = hu - n_q - n_kv;
+        v_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * dv + j] = from_float<T>(y);
+    } else {
+        const int h = hu - n_q;
+        k_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * d + j] = from_float<T>(y);
+    }
 }
 
 // state[slot][s] <- the value (taps - 1 - s) places before the end of the row after this step: one of the step's
@@ -188,20 +211,20 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
     FD_REQUIRE(taps == 1 || state != nullptr, -2, "conv_rope_append: %d taps need a state", taps);
     const int C = (n_q + n_kv) * d + n_kv * dv;
     FD_REQUIRE(ld >= C, -2, "conv_rope_append: rows of %d columns cannot hold %d channels", ld, C);
-    const size_t smem = (size_t)C * sizeof(float);
-    FD_REQUIRE(smem <= 200 * 1024, -2, "conv_rope_append: %d channels need %zu bytes of shared memory (max 200 KB)", C, smem);
-    const int threads = C >= 1024 ? 256 : 128;
+    const int widest = d > dv ? d : dv;
+    FD_REQUIRE(widest <= 1024 && n_q + 2 * n_kv <= 65535, -2, "conv_rope_append: heads of %d channels (max 1024)", widest);
+    const size_t smem = (size_t)widest * sizeof(float);
+    const int threads = (widest + 31) / 32 * 32;
+    const dim3 grid(T, n_q + 2 * n_kv);
     if (dtype == 0) {
         auto k = conv_rope_append_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return launch("conv_rope_append", k, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1), (const float*)proj, ld,
+        return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const float*)proj, ld,
                       conv_w, state, (float*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                       row_q_len, (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q,
                       n_kv, d, dv, taps, write_kv, update_state, status);
     }
     auto k = conv_rope_append_kernel<bf16>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch("conv_rope_append", k, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1), (const bf16*)proj, ld,
+    return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const bf16*)proj, ld,
                   conv_w, state, (bf16*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                   row_q_len, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv,
                   d, dv, taps, write_kv, update_state, status);

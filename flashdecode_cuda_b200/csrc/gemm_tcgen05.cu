@@ -38,10 +38,16 @@ struct TcParams {
     int* status;
     int M, N, K;
     int mode;              // 1: bf16 [M, N]; 2: float [M, N]; 3: gated, bf16 [M, N / 2];
-                           // 4: q/k/v projection with rotary encoding and cache append (TcRope)
+                           // 4: q/k/v projection with rotary encoding and cache append (TcRope);
+                           // 5: bf16 [M, N] = max(x W^T, 0)^2
     int bias_f32;
     unsigned long long wait_ns;   // limit of every bounded wait
     int skip_last;                // tests only: the producer leaves out its very last copy, so that a wait runs out
+    // Grouped form (the persistent one-SM kernel only): W is a stack of matrices [E][N, K]; the 128-row tile t of x
+    // multiplies matrix tile_expert[t], and only the first *n_row_tiles row tiles exist (both live on the device:
+    // a routed feed-forward decides them there).  Null: the plain product.
+    const int* tile_expert = nullptr;
+    const int* n_row_tiles = nullptr;
 };
 
 // Mode 4: where the token of an output row lives in the cache.
@@ -186,7 +192,11 @@ __device__ __forceinline__ void tc_store32(const TcParams& p, const TcRope& ra, 
                                : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[nn]);
         }
     }
-    if (p.mode == 1) {
+    if (p.mode == 5) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { const float r = fmaxf(f[j], 0.f); f[j] = r * r; }
+    }
+    if (p.mode == 1 || p.mode == 5) {
         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n;
         if (cols == 32 && (p.N & 7) == 0) {
 #pragma unroll
@@ -350,7 +360,9 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_iters = (p.K + TC_BK - 1) / TC_BK;
-    const int n_tiles = tiles_m * tiles_n;
+    // the grouped form: only the row tiles that the device-side grouping filled
+    const int tm = p.n_row_tiles != nullptr ? min(tiles_m, *p.n_row_tiles) : tiles_m;
+    const int n_tiles = tm * tiles_n;
 
     if (threadIdx.x == 0) {
         abort_flag[0] = 0;
@@ -379,7 +391,10 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         int it = 0;                                    // k-blocks issued so far, over all tiles
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+            const int m0 = (tile % tm) * TC_BM;
+            // the grouped form: the tile's own matrix of the stack (a box that runs past its last rows reads the next
+            // matrix's, or zeros at the end of the stack: columns the epilogue does not store)
+            const int n0 = (tile / tm) * BN + (p.tile_expert != nullptr ? p.tile_expert[tile % tm] * p.N : 0);
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES && !mbar_wait(s_addr(&empty[s]), ((it / STAGES) - 1) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
@@ -428,7 +443,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         int t = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
             const int buf = t & 1;
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+            const int m0 = (tile % tm) * TC_BM, n0 = (tile / tm) * BN;
             const int m = m0 + quarter * 32 + lane;
             const TcToken tk = tc_token(p, ra, m);
             const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, p.wait_ns)) &&
@@ -642,8 +657,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 int g_tc_wide = 1;      // 2: the two-SM kernel where N >= 256; 1: the persistent one-SM kernel (128 x 256 tiles, or 128 x 128
                         // where those number no more than the SMs); 3: the same with 128 x 256 tiles always; 0: 128 x 128 tiles, one per CTA
 
+// w_stack: matrices in the stack w [w_stack][N, K] (the grouped form; 1: the plain product).
 static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRope& ra, cudaStream_t stream,
-                     const char* what) {
+                     const char* what, int w_stack = 1) {
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
@@ -683,7 +699,7 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
     }
     int rc = tensor_map(x, p.M, p.K, &mx, TC_BM);
     if (rc != 0) return rc;
-    rc = tensor_map(w, p.N, p.K, &mw, (wide && !narrow) ? TW_BN : TC_BM);
+    rc = tensor_map(w, w_stack * p.N, p.K, &mw, (wide && !narrow) ? TW_BN : TC_BM);
     if (rc != 0) return rc;
     if (wide) {
         const int bn = narrow ? TN_BN : TW_BN;
@@ -734,6 +750,29 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
     p.wait_ns = g_tc_wait_ns; p.skip_last = g_tc_skip_last;
     TcRope ra = {};
     return launch_tc(x, w, p, ra, stream, "gemm_tcgen05");
+}
+
+// Grouped product of a routed feed-forward: x [M, K] holds row tiles of 128 (M a multiple of 128) of which the first
+// *n_row_tiles exist; tile t multiplies matrix tile_expert[t] of the stack w [E][N, K] (both on the device).
+// mode 5: out bf16 [M, N] = max(x w_e^T, 0)^2; mode 2: out float [M, N].  N >= 256 (the persistent kernel).
+extern "C" int fd_gemm_tc_grouped(const void* x, const void* w, void* out, int mode, int M, int N, int K, int E,
+                                  const int* tile_expert, const int* n_row_tiles, int* status, cudaStream_t stream) {
+    if (M == 0 || N == 0 || E == 0) return 0;
+    FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    FD_REQUIRE(mode == 5 || mode == 2, -2, "gemm_tcgen05 (grouped): mode %d", mode);
+    FD_REQUIRE(M % TC_BM == 0 && N >= TW_BN && g_tc_wide != 0 && g_tc_wide != 2, -2,
+               "gemm_tcgen05 (grouped): %d rows (whole tiles of %d) and %d columns (at least %d) on the persistent one-SM kernel",
+               M, TC_BM, N, TW_BN);
+    FD_REQUIRE(tile_expert != nullptr && n_row_tiles != nullptr && (long long)E * N < (1ll << 31), -2,
+               "gemm_tcgen05 (grouped): needs the tiles' experts and their number");
+    FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0, -2,
+               "gemm_tcgen05: x, W and out must be 16-byte aligned");
+    TcParams p;
+    p.bias = nullptr; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = 0;
+    p.wait_ns = g_tc_wait_ns; p.skip_last = g_tc_skip_last;
+    p.tile_expert = tile_expert; p.n_row_tiles = n_row_tiles;
+    TcRope ra = {};
+    return launch_tc(x, w, p, ra, stream, "gemm_tcgen05 (grouped)", E);
 }
 
 // The q/k/v projection of a prompt step with bias, rotary encoding and the append to the

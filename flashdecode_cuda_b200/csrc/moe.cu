@@ -24,27 +24,50 @@
 
 namespace fd {
 
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 256;
 constexpr int MOE_MT = 32;          // rows of a tile
 constexpr int MOE_NT = 64;          // columns of a tile
 constexpr int MOE_KT = 32;          // k step
 constexpr int MOE_THREADS = 256;
 
+// A CTA takes one token.  `logits` null: the CTA computes the token's router logits itself (x row in shared memory as
+// float, a warp per output, 16-byte loads, lanes over k); else they are read from logits [T, n_out] (float, made by a
+// matrix product) and only the selection runs.
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
-moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ correction,
-                 int* __restrict__ ids, float* __restrict__ wts, int H, int n_out, int top) {
-    extern __shared__ float z_s[];         // [n_out] logits, then scores; [n_out] choice scores
+moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ logits,
+                 const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ wts, int H, int n_out,
+                 int top) {
+    extern __shared__ __align__(16) float z_s[];         // [n_out] logits, then scores; [n_out] choice scores; [H] the row
     float* c_s = z_s + n_out;
+    float* x_s = c_s + n_out;
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const T* xr = x + (size_t)t * H;
-    for (int o = warp; o < n_out; o += ROUTE_THREADS / 32) {
-        const T* wr = w + (size_t)o * H;
-        float acc = 0.f;
-        for (int k = lane; k < H; k += 32) acc = fmaf(to_float(wr[k]), to_float(xr[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) z_s[o] = acc;
+    if (logits != nullptr) {
+        for (int o = threadIdx.x; o < n_out; o += ROUTE_THREADS) z_s[o] = logits[(size_t)t * n_out + o];
+    } else {
+        const T* xr = x + (size_t)t * H;
+        for (int k = threadIdx.x; k < H; k += ROUTE_THREADS) x_s[k] = to_float(xr[k]);
+        __syncthreads();
+        constexpr int VEC = 16 / sizeof(T);
+        const bool vec = H % VEC == 0 && (uintptr_t)w % 16 == 0;
+        for (int o = warp; o < n_out; o += ROUTE_THREADS / 32) {
+            const T* wr = w + (size_t)o * H;
+            float acc = 0.f;
+            if (vec) {
+#pragma unroll 4
+                for (int c = lane; c < H / VEC; c += 32) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(wr + c * VEC);
+                    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), x_s[c * VEC + j], acc);
+                }
+            } else {
+                for (int k = lane; k < H; k += 32) acc = fmaf(to_float(wr[k]), x_s[k], acc);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) z_s[o] = acc;
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -326,6 +349,19 @@ static int launch_moe_mma(const void* a, const void* w, void* out, const int* so
                   (const __nv_bfloat16*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K);
 }
 
+// xs[row] = x[sorted_pair[row] / top] for the grouped rows that exist, zeros for the padding rows among them: the
+// grouped rows as one contiguous matrix, for products that read their operands through tensor maps.
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ xs,
+                                  const int* __restrict__ sorted_pair, const int* __restrict__ n_tiles, int mt, int top,
+                                  int K8) {
+    const int row = blockIdx.x;
+    if (row >= *n_tiles * mt) return;
+    const int pr = sorted_pair[row];
+    const uint4* src = pr < 0 ? nullptr : reinterpret_cast<const uint4*>(x) + (size_t)(pr / top) * K8;
+    uint4* dst = reinterpret_cast<uint4*>(xs) + (size_t)row * K8;
+    for (int c = threadIdx.x; c < K8; c += blockDim.x) dst[c] = src != nullptr ? src[c] : make_uint4(0, 0, 0, 0);
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ x, const T* __restrict__ shared,
                                    const int* __restrict__ ids, const float* __restrict__ wts,
@@ -357,19 +393,22 @@ typedef __nv_bfloat16 bf16;
 // bfloat16 steps with many rows per expert.
 extern "C" int fd_moe_tile_rows(int dtype, int rows_per_expert) { return dtype == 1 && rows_per_expert >= 96 ? 128 : MOE_MT; }
 
-// x [T, H] and w [n_out, H] of type dtype (0 float32, 1 bfloat16); correction [n_out] float or null;
-// ids [T, top] int32 and wts [T, top] float come back.
-extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float* correction, int* ids, float* wts,
-                            int T, int H, int n_out, int top, cudaStream_t stream) {
+// x [T, H] and w [n_out, H] of type dtype (0 float32, 1 bfloat16), or logits [T, n_out] float made from them by a
+// matrix product (then x and w are not read); correction [n_out] float or null; ids [T, top] int32 and wts [T, top]
+// float come back.
+extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float* logits, const float* correction,
+                            int* ids, float* wts, int T, int H, int n_out, int top, cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(n_out >= 1 && top >= 1 && top <= n_out && n_out <= 4096, -2,
                "moe_route: %d choices of %d router outputs (at most 4096)", top, n_out);
-    const size_t smem = 2 * (size_t)n_out * sizeof(float);
+    const size_t smem = (2 * (size_t)n_out + (logits ? 0 : H)) * sizeof(float);
+    FD_REQUIRE(smem <= 48 * 1024, -2, "moe_route: a row of %d and %d outputs need %zu bytes of shared memory (max 48 KB); "
+               "give the logits", H, n_out, smem);
     if (dtype == 0)
         return launch("moe_route", moe_route_kernel<float>, dim3(T), dim3(ROUTE_THREADS), smem, stream, dim3(1, 1, 1),
-                      (const float*)x, (const float*)w, correction, ids, wts, H, n_out, top);
+                      (const float*)x, (const float*)w, logits, correction, ids, wts, H, n_out, top);
     return launch("moe_route", moe_route_kernel<bf16>, dim3(T), dim3(ROUTE_THREADS), smem, stream, dim3(1, 1, 1),
-                  (const bf16*)x, (const bf16*)w, correction, ids, wts, H, n_out, top);
+                  (const bf16*)x, (const bf16*)w, logits, correction, ids, wts, H, n_out, top);
 }
 
 // cap: rows of the grouped buffers, at least P rounded up to whole tiles plus one tile per expert.
@@ -413,6 +452,15 @@ extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, i
     if (mode == 0) FD_MG(bf16, 0);
     FD_MG(bf16, 1);
 #undef FD_MG
+}
+
+// xs [cap, K] <- the rows of x [T, K] (bfloat16, K a multiple of 8) in grouped order.
+extern "C" int fd_moe_gather(const void* x, void* xs, const int* sorted_pair, const int* n_tiles, int cap, int mt,
+                             int top, int K, cudaStream_t stream) {
+    if (cap == 0) return 0;
+    FD_REQUIRE(K % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)xs % 16 == 0, -2, "moe_gather: rows of %d need 16-byte chunks", K);
+    return launch("moe_gather", moe_gather_kernel, dim3(cap), dim3(K / 8 >= 256 ? 256 : 128), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)x, (bf16*)xs, sorted_pair, n_tiles, mt, top, K / 8);
 }
 
 extern "C" int fd_moe_combine(const float* y, const void* x, const void* shared, const int* ids, const float* wts,

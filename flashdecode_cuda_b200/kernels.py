@@ -101,10 +101,12 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_add_concat": [P, I, P, P, P, I, I, I, P],
         "fd_relu2": [P, P, I, LL, P],
         "fd_moe_tile_rows": [I, I],
-        "fd_moe_route": [P, P, I, P, P, P, I, I, I, I, P],
+        "fd_moe_route": [P, P, I, P, P, P, P, I, I, I, I, P],
         "fd_moe_align": [P, I, I, P, P, P, P, I, I, P],
         "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, P],
         "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "fd_moe_gather": [P, P, P, P, I, I, I, I, P],
+        "fd_gemm_tc_grouped": [P, P, P, I, I, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
         "fd_copy_d2h_sync": [P, P, LL, P],
@@ -628,18 +630,23 @@ def moe_grouped_rows(n_pairs: int, n_experts: int, mt: int) -> int:
     return -(-worst // mt) * mt
 
 
+ROUTE_FUSED_MAX_ROW = 8192      # widest row of x the routing kernel takes into shared memory to make its own logits
+
+
 def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
-              wts: torch.Tensor) -> None:
+              wts: torch.Tensor, logits: Optional[torch.Tensor] = None) -> None:
     """Per row of x [T, H]: softmax scores over the rows of ``router`` [n_out, H] (float arithmetic), the ``top``
     outputs with the largest score + correction into ``ids`` [T, top] (int32), and their scores over their sum
-    (+ 1e-20) into ``wts`` [T, top] (float32)."""
+    (+ 1e-20) into ``wts`` [T, top] (float32).  ``logits`` [T, n_out] float32: the router's outputs made by a matrix
+    product beforehand (steps of many tokens); without them the kernel makes them itself, a token per CTA."""
     T, H = x.shape
     n_out, top = router.shape[0], ids.shape[1]
     assert router.shape == (n_out, H) and router.dtype == x.dtype and ids.dtype == torch.int32
     assert wts.dtype == torch.float32 and wts.shape == ids.shape == (T, top)
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n_out)
-    _check(lib().fd_moe_route(_ptr(x), _ptr(router), _dt(x.dtype), _ptr(correction), _ptr(ids), _ptr(wts), T, H, n_out,
-                              top, _stream()))
+    assert logits is None or (logits.dtype == torch.float32 and logits.shape == (T, n_out))
+    _check(lib().fd_moe_route(_ptr(x), _ptr(router), _dt(x.dtype), _ptr(logits), _ptr(correction), _ptr(ids), _ptr(wts),
+                              T, H, n_out, top, _stream()))
 
 
 def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_pair: torch.Tensor,
@@ -666,6 +673,33 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, so
     assert out.dtype == (torch.float32 if down else a.dtype) and (not down or a.shape[0] == cap)
     _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), int(down), _ptr(sorted_pair), _ptr(tile_expert),
                              _ptr(n_tiles), cap, mt, top, N, Kd, _stream()))
+
+
+def moe_gather(x: torch.Tensor, xs: torch.Tensor, sorted_pair: torch.Tensor, n_tiles: torch.Tensor, top: int,
+               mt: int) -> None:
+    """xs [cap, K] <- the rows of x [T, K] in grouped order (zeros in padding rows; rows beyond the tiles that exist are
+    left alone): the operand of ``gemm_tc_grouped``, which reads through a tensor map."""
+    cap, Kd = xs.shape
+    assert x.dtype == xs.dtype == torch.bfloat16 and x.shape[1] == Kd and sorted_pair.numel() == cap
+    _check(lib().fd_moe_gather(_ptr(x), _ptr(xs), _ptr(sorted_pair), _ptr(n_tiles), cap, mt, top, Kd, _stream()))
+
+
+def gemm_tc_grouped_supported(N: int, K: int) -> bool:
+    """Whether the grouped tcgen05 product takes matrices [N, K]."""
+    return N >= 256 and gemm_tc_supported(128, N, K)
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, relu2: bool, tile_expert: torch.Tensor,
+                    n_tiles: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """Grouped product on the tcgen05 tensor cores: x [cap, K] in row tiles of 128 of which the first ``n_tiles``
+    exist, tile t times matrix ``tile_expert[t]`` of the stack w [E, N, K] (both device tensors).  ``relu2``: out
+    bfloat16 [cap, N] = max(x w_e^T, 0)^2; else out float32 [cap, N]."""
+    cap, Kd = x.shape
+    E, N, _ = w.shape
+    assert x.dtype == w.dtype == torch.bfloat16 and w.shape[2] == Kd and out.shape == (cap, N) and cap % 128 == 0
+    assert out.dtype == (torch.bfloat16 if relu2 else torch.float32) and tile_expert.numel() * 128 >= cap
+    _check(lib().fd_gemm_tc_grouped(_ptr(x), _ptr(w), _ptr(out), 5 if relu2 else 2, cap, N, Kd, E, _ptr(tile_expert),
+                                    _ptr(n_tiles), _ptr(status), _stream()))
 
 
 def moe_combine(y: Optional[torch.Tensor], x: torch.Tensor, shared: Optional[torch.Tensor], ids: torch.Tensor,

@@ -12,6 +12,14 @@ from ..weights.spec import TensorSpec
 from .base import FeedForward, Runtime
 from .linear import matmul
 
+# Up to this many tokens the routing kernel makes the router's logits itself (one launch, a CTA per token, each reading
+# the whole router matrix); above it they come from a matrix product.
+ROUTE_FUSED_MAX_TOKENS = 64
+# Which kernel takes the grouped products of steps with many rows per expert in bfloat16: "auto": the TMA + tcgen05
+# kernel where it takes the sizes (expert matrices of at least 256 rows), else the mma.sync kernel; "mma": the
+# mma.sync kernel always (tests run both).
+GROUPED_GEMM = "auto"
+
 
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
@@ -82,7 +90,14 @@ class RoutedExperts(FeedForward):
         T, ws, H, top = ctx.T, ctx.ws, self.hidden_size, self.top
         ids = ws.get("moe_ids", (T, top), torch.int32)
         wts = ws.get("moe_wts", (T, top), torch.float32)
-        K.moe_route(x, self.router, self.correction, ids, wts)
+        logits = None
+        if x.dtype == torch.float32 or T > ROUTE_FUSED_MAX_TOKENS or H > K.ROUTE_FUSED_MAX_ROW:
+            # many tokens: the logits as one product (float32 out: bfloat16 operands multiply exactly, sums are float).
+            # float32 always takes this way: its product sums k in one fixed order whatever the step holds, so a
+            # token's scores do not change by a bit with its neighbours
+            logits = ws.get("moe_logits", (T, self.router.shape[0]), torch.float32)
+            matmul(x, self.router, None, logits, status=self.rt.status)
+        K.moe_route(x, self.router, self.correction, ids, wts, logits)
         shared = None
         if self.s_up is not None:
             h = ws.get("moe_shared_h", (T, self.shared_ff), x.dtype)
@@ -100,9 +115,17 @@ class RoutedExperts(FeedForward):
             n_tiles = ws.get("moe_n_tiles", (1,), torch.int32)
             K.moe_align(ids, self.E, pair_pos, sorted_pair, tile_expert, n_tiles, mt)
             act = ws.get("moe_act", (cap, self.ff), x.dtype)
-            K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
             y = ws.get("moe_y", (cap, H), torch.float32)
-            K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top, mt)
+            if (mt == 128 and GROUPED_GEMM == "auto" and K.gemm_tc_grouped_supported(self.ff, H)
+                    and K.gemm_tc_grouped_supported(H, self.ff)):
+                # prompts: the grouped rows as one matrix, then both products on the tcgen05 tensor cores
+                xs = ws.get("moe_xs", (cap, H), x.dtype)
+                K.moe_gather(x, xs, sorted_pair, n_tiles, top, mt)
+                K.gemm_tc_grouped(xs, self.w_up, act, True, tile_expert, n_tiles, self.rt.status)
+                K.gemm_tc_grouped(act, self.w_down, y, False, tile_expert, n_tiles, self.rt.status)
+            else:
+                K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
+                K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top, mt)
         out = ws.get("ffn_out", (T, H), x.dtype)
         K.moe_combine(y, x, shared, ids, wts, pair_pos, out, self.E)
         return out

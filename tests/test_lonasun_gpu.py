@@ -238,6 +238,49 @@ def test_routed_experts(dtype, E, n_id, top, H, ff, T):
     assert rel_err(out, want) < KTOL[dtype]
 
 
+@pytest.mark.parametrize("E,H,ff,T,top", [(3, 256, 384, 300, 2), (5, 320, 256, 700, 3), (2, 512, 768, 150, 2)])
+def test_grouped_products_on_tcgen05_equal_the_plain_experts(E, H, ff, T, top):
+    """Prompts in bfloat16: the grouped rows gathered into one matrix, then both products by the TMA + tcgen05 kernel
+    with the tile's expert looked up on the device; against the plain experts row by row, and with row tiles that do
+    not exist left alone."""
+    torch.manual_seed(E + T)
+    dt = torch.bfloat16
+    x = torch.randn(T, H).to(dt)
+    w_up = (torch.randn(E, ff, H) / H ** 0.5).to(dt)
+    w_down = (torch.randn(E, H, ff) / ff ** 0.5).to(dt)
+    ids = torch.stack([torch.randperm(E + 1)[:top] for _ in range(T)]).to(torch.int32)      # output E: an identity expert
+    mt = K.moe_tile_rows(dt, T * top, E, (H, ff))
+    assert mt == 128
+    cap = K.moe_grouped_rows(T * top, E, mt)
+    pair_pos = torch.zeros(T * top, dtype=torch.int32, device=DEV)
+    sorted_pair = torch.zeros(cap, dtype=torch.int32, device=DEV)
+    tile_expert = torch.zeros(cap // mt, dtype=torch.int32, device=DEV)
+    n_tiles = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.moe_align(ids.to(DEV), E, pair_pos, sorted_pair, tile_expert, n_tiles, mt)
+    xs = torch.full((cap, H), 7.0, dtype=dt, device=DEV)
+    act = torch.full((cap, ff), 7.0, dtype=dt, device=DEV)
+    y = torch.full((cap, H), 7.0, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.moe_gather(x.to(DEV), xs, sorted_pair, n_tiles, top, mt)
+    K.gemm_tc_grouped(xs, w_up.to(DEV), act, True, tile_expert, n_tiles, status)
+    K.gemm_tc_grouped(act, w_down.to(DEV), y, False, tile_expert, n_tiles, status)
+    assert int(status.item()) == 0
+    used = int(n_tiles.item()) * mt
+    assert used < cap and bool((y[used:] == 7.0).all()) and bool((xs[used:] == 7.0).all())
+    pp, yc = pair_pos.cpu(), y.cpu().double()
+    worst = 0.0
+    scale = 0.0
+    for p in range(0, T * top, 7):
+        e = int(ids.view(-1)[p])
+        if e >= E:
+            assert int(pp[p]) == -1
+            continue
+        want = P.relu2_expert(x[p // top].double(), w_up[e].double(), w_down[e].double())
+        worst = max(worst, float((yc[int(pp[p])] - want).abs().max()))
+        scale = max(scale, float(want.abs().max()))
+    assert worst / scale < KTOL["bfloat16"]
+
+
 # ---------------------------------------------------------------- whole models
 class Folders(dict):
     """Model folders by (name, dtype): in bfloat16 the routers' choice is fixed by their corrections (see
