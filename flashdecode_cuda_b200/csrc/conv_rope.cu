@@ -25,10 +25,11 @@ namespace fd {
 
 constexpr int CONV_MAX_TAPS = 8;      // more taps than this take the loop that loads one value at a time
 
-// A CTA takes one head (of q, k or v) of one token; a thread one channel of it: it loads the values its taps see
-// (independent loads, issued together), convolves, leaves the result in shared memory for its rotation partner, rotates
-// and stores.  In a step of single tokens the same thread also moves the channel's state on: it holds the old state in
-// registers already.
+// A CTA takes one head (of q, k or v) of `tpc` consecutive tokens of the step, one after another; a thread one channel
+// of it: it loads the values its taps see (independent loads, issued together), convolves, leaves the result in shared
+// memory for its rotation partner, rotates and stores.  In a step of single tokens the same thread also moves the
+// channel's state on: it holds the old state in registers already.  (One token per CTA in a prompt step of 2,048
+// tokens meant 49,000 CTAs of a few loads each, 70 us of which most was their scheduling.)
 template <typename T>
 __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
                                         float* __restrict__ state, T* __restrict__ q_out,
@@ -39,12 +40,14 @@ __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, cons
                                         T* __restrict__ k_pool, T* __restrict__ v_pool,
                                         const int* __restrict__ block_table, int max_blocks, int num_blocks,
                                         int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
-                                        int update_state, int* status) {
+                                        int update_state, int* status, int n_tok, int tpc) {
     extern __shared__ float y_s[];                 // the head's convolved channels
-    const int t = blockIdx.x, hu = blockIdx.y;     // head unit: q heads, then k heads, then v heads
+    const int hu = blockIdx.y;                     // head unit: q heads, then k heads, then v heads
+  for (int t = blockIdx.x * tpc; t < min(n_tok, (int)(blockIdx.x + 1) * tpc); ++t) {
+    __syncthreads();                               // the token before is done with y_s
     const int r = tok_row[t];
     const int slot = row_slot[r];
-    if (slot < 0) return;                          // padding row
+    if (slot < 0) continue;                        // padding row
     const int C = (n_q + n_kv) * d + n_kv * dv;
     const bool is_v = hu >= n_q + n_kv;
     const int width = is_v ? dv : d;
@@ -95,7 +98,7 @@ __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, cons
         y_s[j] = y;
     }
     __syncthreads();
-    if (j >= width) return;
+    if (j >= width) continue;
 
     const int half = rot >> 1;
     const bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
@@ -108,14 +111,14 @@ __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, cons
     }
     if (hu < n_q) {
         q_out[(size_t)t * n_q * d + c0 + j] = from_float<T>(y);
-        return;
+        continue;
     }
-    if (!write_kv || pos < 0) return;
+    if (!write_kv || pos < 0) continue;
     const int col = pos / block_size;
     const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
     if (blk < 0 || blk >= num_blocks) {
         if (j == 0) set_status(status, STATUS_BAD_BLOCK);
-        return;
+        continue;
     }
     if (is_v) {
         const int h = hu - n_q - n_kv;
@@ -124,6 +127,7 @@ __global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, cons
         const int h = hu - n_q;
         k_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * d + j] = from_float<T>(y);
     }
+  }
 }
 
 // state[slot][s] <- the value (taps - 1 - s) places before the end of the row after this step: one of the step's
@@ -215,19 +219,20 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
     FD_REQUIRE(widest <= 1024 && n_q + 2 * n_kv <= 65535, -2, "conv_rope_append: heads of %d channels (max 1024)", widest);
     const size_t smem = (size_t)widest * sizeof(float);
     const int threads = (widest + 31) / 32 * 32;
-    const dim3 grid(T, n_q + 2 * n_kv);
+    const int tpc = T > 64 ? 8 : 1;               // tokens a CTA takes, one after another
+    const dim3 grid((T + tpc - 1) / tpc, n_q + 2 * n_kv);
     if (dtype == 0) {
         auto k = conv_rope_append_kernel<float>;
         return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const float*)proj, ld,
                       conv_w, state, (float*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                       row_q_len, (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q,
-                      n_kv, d, dv, taps, write_kv, update_state, status);
+                      n_kv, d, dv, taps, write_kv, update_state, status, T, tpc);
     }
     auto k = conv_rope_append_kernel<bf16>;
     return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const bf16*)proj, ld,
                   conv_w, state, (bf16*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                   row_q_len, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv,
-                  d, dv, taps, write_kv, update_state, status);
+                  d, dv, taps, write_kv, update_state, status, T, tpc);
 }
 
 extern "C" int fd_conv_state_update(const void* proj, int ld, int dtype, float* state, const int* row_slot,

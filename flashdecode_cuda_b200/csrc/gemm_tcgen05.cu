@@ -736,12 +736,12 @@ extern "C" int fd_gemm_tc_supported(int M, int N, int K) {
 }
 
 // mode 1: out bf16 [M, N] (+ bias); 2: out float [M, N] (+ bias); 3: W rows in tiles of 8 gate +
-// 8 up rows, out bf16 [M, N / 2] = silu(gate) * up (N a multiple of 16).
+// 8 up rows, out bf16 [M, N / 2] = silu(gate) * up (N a multiple of 16); 5: out bf16 [M, N] = max(x W^T (+ bias), 0)^2.
 extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bias_f32, void* out, int mode,
                           int M, int N, int K, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
-    FD_REQUIRE(mode >= 1 && mode <= 3, -2, "gemm_tcgen05: mode %d", mode);
+    FD_REQUIRE((mode >= 1 && mode <= 3) || mode == 5, -2, "gemm_tcgen05: mode %d", mode);
     FD_REQUIRE(mode != 3 || N % 16 == 0, -2, "gemm_tcgen05: the gated form needs N (= 2 x outputs) to be a multiple of 16, got %d", N);
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0, -2,
                "gemm_tcgen05: x, W and out must be 16-byte aligned");
@@ -754,12 +754,13 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
 
 // Grouped product of a routed feed-forward: x [M, K] holds row tiles of 128 (M a multiple of 128) of which the first
 // *n_row_tiles exist; tile t multiplies matrix tile_expert[t] of the stack w [E][N, K] (both on the device).
-// mode 5: out bf16 [M, N] = max(x w_e^T, 0)^2; mode 2: out float [M, N].  N >= 256 (the persistent kernel).
+// mode 5: out bf16 [M, N] = max(x w_e^T, 0)^2; mode 1: out bf16 [M, N]; mode 2: out float [M, N].  N >= 256 (the
+// persistent kernel).
 extern "C" int fd_gemm_tc_grouped(const void* x, const void* w, void* out, int mode, int M, int N, int K, int E,
                                   const int* tile_expert, const int* n_row_tiles, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0 || E == 0) return 0;
     FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
-    FD_REQUIRE(mode == 5 || mode == 2, -2, "gemm_tcgen05 (grouped): mode %d", mode);
+    FD_REQUIRE(mode == 5 || mode == 2 || mode == 1, -2, "gemm_tcgen05 (grouped): mode %d", mode);
     FD_REQUIRE(M % TC_BM == 0 && N >= TW_BN && g_tc_wide != 0 && g_tc_wide != 2, -2,
                "gemm_tcgen05 (grouped): %d rows (whole tiles of %d) and %d columns (at least %d) on the persistent one-SM kernel",
                M, TC_BM, N, TW_BN);

@@ -8,7 +8,7 @@
 //    every tile and the number of tiles;
 //  * moe_gemm: one CTA per (row tile, column tile): rows gathered through the
 //    grouping, the tile's expert's matrix; epilogue relu^2 into the grouped
-//    activations, or float rows for the combine.  float32: CUDA cores, k ascending
+//    activations, or plain rows for the combine.  float32: CUDA cores, k ascending
 //    in one fmaf chain per output (no bit depends on what else is in the step);
 //    bfloat16: tensor cores (mma.m16n8k16, float accumulators, cp.async ring of
 //    three 64-deep k-blocks, swizzled tiles), row tiles of 32 for steps of few
@@ -24,7 +24,7 @@
 
 namespace fd {
 
-constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_THREADS = 1024;     // a warp per router output when the kernel makes the logits itself (one warp selects)
 constexpr int MOE_MT = 32;          // rows of a tile
 constexpr int MOE_NT = 64;          // columns of a tile
 constexpr int MOE_KT = 32;          // k step
@@ -44,18 +44,18 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* 
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (logits != nullptr) {
-        for (int o = threadIdx.x; o < n_out; o += ROUTE_THREADS) z_s[o] = logits[(size_t)t * n_out + o];
+        for (int o = threadIdx.x; o < n_out; o += blockDim.x) z_s[o] = logits[(size_t)t * n_out + o];
     } else {
         const T* xr = x + (size_t)t * H;
-        for (int k = threadIdx.x; k < H; k += ROUTE_THREADS) x_s[k] = to_float(xr[k]);
+        for (int k = threadIdx.x; k < H; k += blockDim.x) x_s[k] = to_float(xr[k]);
         __syncthreads();
         constexpr int VEC = 16 / sizeof(T);
         const bool vec = H % VEC == 0 && (uintptr_t)w % 16 == 0;
-        for (int o = warp; o < n_out; o += ROUTE_THREADS / 32) {
+        for (int o = warp; o < n_out; o += blockDim.x >> 5) {
             const T* wr = w + (size_t)o * H;
             float acc = 0.f;
             if (vec) {
-#pragma unroll 4
+#pragma unroll 8
                 for (int c = lane; c < H / VEC; c += 32) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(wr + c * VEC);
                     const T* e = reinterpret_cast<const T*>(&raw);
@@ -158,7 +158,7 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int*
 }
 
 // MODE 0: a[row] = x[sorted_pair[row] / top], out = relu(acc)^2 as T into act [cap, N]
-// MODE 1: a[row] = act[row],                  out = acc as float into y [cap, N]
+// MODE 1: a[row] = act[row],                  out = acc as T into y [cap, N]
 template <typename T, int MODE>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restrict__ out,
@@ -216,7 +216,7 @@ moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restri
                 const float v = fmaxf(acc[i][j], 0.f);
                 static_cast<T*>(out)[orow + c] = from_float<T>(v * v);
             } else {
-                static_cast<float*>(out)[orow + c] = acc[i][j];
+                static_cast<T*>(out)[orow + c] = from_float<T>(acc[i][j]);
             }
         }
     }
@@ -320,13 +320,11 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
                 if (MODE == 0) {
                     v0 = fmaxf(v0, 0.f); v0 *= v0;
                     v1 = fmaxf(v1, 0.f); v1 *= v1;
+                }
+                {
                     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out) + orow + c;
                     if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v0, v1);
                     else { if (c < N) o[0] = __float2bfloat16_rn(v0); if (c + 1 < N) o[1] = __float2bfloat16_rn(v1); }
-                } else {
-                    float* o = static_cast<float*>(out) + orow + c;
-                    if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
-                    else { if (c < N) o[0] = v0; if (c + 1 < N) o[1] = v1; }
                 }
             }
         }
@@ -362,22 +360,65 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, __nv_bflo
     for (int c = threadIdx.x; c < K8; c += blockDim.x) dst[c] = src != nullptr ? src[c] : make_uint4(0, 0, 0, 0);
 }
 
+__device__ __forceinline__ void load4(const float* p, float v[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float v[4]) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+
+constexpr int COMBINE_MAX_TOP = 64;       // choices per token whose rows, weights and places the combine keeps in shared memory
+
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ x, const T* __restrict__ shared,
+__global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ shared,
                                    const int* __restrict__ ids, const float* __restrict__ wts,
                                    const int* __restrict__ pair_pos, T* __restrict__ out, int H, int top, int E) {
+    __shared__ int pos_s[COMBINE_MAX_TOP];        // row of y, -1: the token's own input (identity), -2: nothing
+    __shared__ float w_s[COMBINE_MAX_TOP];
     const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < top; c += blockDim.x) {
+        const size_t p = t * top + c;
+        w_s[c] = wts[p];
+        const int pp = pair_pos[p];
+        pos_s[c] = ids[p] >= E ? -1 : (pp >= 0 ? pp : -2);
+    }
+    __syncthreads();
+    // four columns per thread where the rows allow 16-byte loads of y
+    if ((H & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float xv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xv[j] = to_float(x[t * H + i + j]);
+            for (int c = 0; c < top; ++c) {
+                const int pos = pos_s[c];
+                const float wgt = w_s[c];
+                if (pos == -1) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] = fmaf(wgt, xv[j], acc[j]);
+                } else if (pos >= 0) {
+                    float v[4];
+                    load4(y + (size_t)pos * H + i, v);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] = fmaf(wgt, v[j], acc[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (shared != nullptr) acc[j] += to_float(shared[t * H + i + j]);
+                out[t * H + i + j] = from_float<T>(acc[j]);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float acc = 0.f;
         for (int c = 0; c < top; ++c) {
-            const size_t p = t * top + c;
-            const float wgt = wts[p];
-            if (ids[p] >= E) {
-                acc = fmaf(wgt, to_float(x[t * H + i]), acc);
-            } else {
-                const int pos = pair_pos[p];
-                if (pos >= 0) acc = fmaf(wgt, y[(size_t)pos * H + i], acc);
-            }
+            const int pos = pos_s[c];
+            if (pos == -1) acc = fmaf(w_s[c], to_float(x[t * H + i]), acc);
+            else if (pos >= 0) acc = fmaf(w_s[c], to_float(y[(size_t)pos * H + i]), acc);
         }
         if (shared != nullptr) acc += to_float(shared[t * H + i]);
         out[t * H + i] = from_float<T>(acc);
@@ -404,10 +445,11 @@ extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float
     const size_t smem = (2 * (size_t)n_out + (logits ? 0 : H)) * sizeof(float);
     FD_REQUIRE(smem <= 48 * 1024, -2, "moe_route: a row of %d and %d outputs need %zu bytes of shared memory (max 48 KB); "
                "give the logits", H, n_out, smem);
+    const int threads = logits != nullptr ? 32 : (n_out >= 32 ? ROUTE_THREADS : ((n_out + 7) / 8 * 8) * 32);
     if (dtype == 0)
-        return launch("moe_route", moe_route_kernel<float>, dim3(T), dim3(ROUTE_THREADS), smem, stream, dim3(1, 1, 1),
+        return launch("moe_route", moe_route_kernel<float>, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1),
                       (const float*)x, (const float*)w, logits, correction, ids, wts, H, n_out, top);
-    return launch("moe_route", moe_route_kernel<bf16>, dim3(T), dim3(ROUTE_THREADS), smem, stream, dim3(1, 1, 1),
+    return launch("moe_route", moe_route_kernel<bf16>, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1),
                   (const bf16*)x, (const bf16*)w, logits, correction, ids, wts, H, n_out, top);
 }
 
@@ -424,7 +466,7 @@ extern "C" int fd_moe_align(const int* ids, int P, int E, int* pair_pos, int* so
                   ids, P, E, pair_pos, sorted_pair, tile_expert, n_tiles, cap, mt);
 }
 
-// mode 0: a = x [T, K], out = act [cap, N] (dtype) = relu(x W_e^T)^2;  mode 1: a = act [cap, K], out = y [cap, N] float.
+// mode 0: a = x [T, K], out = act [cap, N] (dtype) = relu(x W_e^T)^2;  mode 1: a = act [cap, K], out = y [cap, N] (dtype).
 // w [E, N, K].
 // mt: the tile rows the grouping was made with.
 extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, int mode, const int* sorted_pair,
@@ -463,14 +505,16 @@ extern "C" int fd_moe_gather(const void* x, void* xs, const int* sorted_pair, co
                   (const bf16*)x, (bf16*)xs, sorted_pair, n_tiles, mt, top, K / 8);
 }
 
-extern "C" int fd_moe_combine(const float* y, const void* x, const void* shared, const int* ids, const float* wts,
+extern "C" int fd_moe_combine(const void* y, const void* x, const void* shared, const int* ids, const float* wts,
                               const int* pair_pos, void* out, int dtype, int T, int H, int top, int E,
                               cudaStream_t stream) {
     if (T == 0) return 0;
+    FD_REQUIRE(top <= COMBINE_MAX_TOP, -2, "moe_combine: %d choices per token (at most %d)", top, COMBINE_MAX_TOP);
+    FD_REQUIRE((uintptr_t)y % 16 == 0, -2, "moe_combine: the experts' rows must be 16-byte aligned");
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == 0)
-        return launch("moe_combine", moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), y,
-                      (const float*)x, (const float*)shared, ids, wts, pair_pos, (float*)out, H, top, E);
-    return launch("moe_combine", moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), y,
-                  (const bf16*)x, (const bf16*)shared, ids, wts, pair_pos, (bf16*)out, H, top, E);
+        return launch("moe_combine", moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
+                      (const float*)y, (const float*)x, (const float*)shared, ids, wts, pair_pos, (float*)out, H, top, E);
+    return launch("moe_combine", moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)y, (const bf16*)x, (const bf16*)shared, ids, wts, pair_pos, (bf16*)out, H, top, E);
 }

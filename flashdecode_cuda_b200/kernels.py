@@ -334,18 +334,24 @@ def gemm_tc_supported(M: int, N: int, K: int) -> bool:
     return bool(lib().fd_gemm_tc_supported(M, N, K))
 
 
+GEMM_RELU2 = 5
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, gated: bool = False,
-            status: Optional[torch.Tensor] = None) -> None:
+            status: Optional[torch.Tensor] = None, relu2: bool = False) -> None:
     """out = x w^T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory); bfloat16 operands, ``out`` bfloat16 or float32 [M, N], or
     with ``gated`` (w rows in tiles of 8 gate + 8 up) bfloat16 [M, N / 2] =
-    silu(gate) * up.  Any M and N; K a multiple of 8."""
+    silu(gate) * up, or with ``relu2`` bfloat16 [M, N] = max(x w^T, 0)^2.  Any M and N; K a multiple of 8."""
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K
     if gated:
         assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and bias is None
         mode = GEMV_GATED
+    elif relu2:
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N)
+        mode = GEMM_RELU2
     else:
         assert out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
         mode = GEMV_BF16 if out.dtype == torch.bfloat16 else GEMV_F32
@@ -665,12 +671,12 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, so
              tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int) -> None:
     """Grouped product with the experts' stacked matrices w [E, N, K].  ``down`` False: a = x [T, K] (rows gathered
     through the grouping), out [cap, N] = relu(x w_e^T)^2 in a's dtype; True: a = the grouped activations [cap, K],
-    out [cap, N] float32.  ``mt``: the tile rows the grouping was made with.  bfloat16 with K a multiple of 8 runs on
+    out [cap, N] in a's dtype.  ``mt``: the tile rows the grouping was made with.  bfloat16 with K a multiple of 8 runs on
     the tensor cores, everything else on the CUDA cores (tiles of 32 rows only)."""
     E, N, Kd = w.shape
     cap = sorted_pair.numel()
     assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N)
-    assert out.dtype == (torch.float32 if down else a.dtype) and (not down or a.shape[0] == cap)
+    assert out.dtype == a.dtype and (not down or a.shape[0] == cap)
     _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), int(down), _ptr(sorted_pair), _ptr(tile_expert),
                              _ptr(n_tiles), cap, mt, top, N, Kd, _stream()))
 
@@ -693,12 +699,13 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, relu2: 
                     n_tiles: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
     """Grouped product on the tcgen05 tensor cores: x [cap, K] in row tiles of 128 of which the first ``n_tiles``
     exist, tile t times matrix ``tile_expert[t]`` of the stack w [E, N, K] (both device tensors).  ``relu2``: out
-    bfloat16 [cap, N] = max(x w_e^T, 0)^2; else out float32 [cap, N]."""
+    bfloat16 [cap, N] = max(x w_e^T, 0)^2; else out bfloat16 or float32 [cap, N]."""
     cap, Kd = x.shape
     E, N, _ = w.shape
     assert x.dtype == w.dtype == torch.bfloat16 and w.shape[2] == Kd and out.shape == (cap, N) and cap % 128 == 0
-    assert out.dtype == (torch.bfloat16 if relu2 else torch.float32) and tile_expert.numel() * 128 >= cap
-    _check(lib().fd_gemm_tc_grouped(_ptr(x), _ptr(w), _ptr(out), 5 if relu2 else 2, cap, N, Kd, E, _ptr(tile_expert),
+    assert out.dtype in ((torch.bfloat16,) if relu2 else (torch.bfloat16, torch.float32)) and tile_expert.numel() * 128 >= cap
+    mode = 5 if relu2 else (1 if out.dtype == torch.bfloat16 else 2)
+    _check(lib().fd_gemm_tc_grouped(_ptr(x), _ptr(w), _ptr(out), mode, cap, N, Kd, E, _ptr(tile_expert),
                                     _ptr(n_tiles), _ptr(status), _stream()))
 
 
@@ -708,7 +715,7 @@ def moe_combine(y: Optional[torch.Tensor], x: torch.Tensor, shared: Optional[tor
     T, H = x.shape
     top = ids.shape[1]
     assert out.shape == x.shape and out.dtype == x.dtype and (shared is None or shared.shape == x.shape)
-    assert y is None or (y.dtype == torch.float32 and y.shape[1] == H)
+    assert y is None or (y.dtype == x.dtype and y.shape[1] == H)
     _check(lib().fd_moe_combine(_ptr(y), _ptr(x), _ptr(shared), _ptr(ids), _ptr(wts), _ptr(pair_pos), _ptr(out),
                                 _dt(x.dtype), T, H, top, n_experts, _stream()))
 

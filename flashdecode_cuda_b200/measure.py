@@ -19,7 +19,8 @@ from . import kernels as K
 
 LAUNCHERS = ["embed", "add_rmsnorm", "silu_mul", "rope_append", "gemv_qkv_rope", "gemm_tc_qkv_rope", "gemm_tc",
              "gemm_stream", "gemm_stream_qkv_rope", "gemv", "gemm_simt", "attention", "conv_rope_append",
-             "conv_state_update", "gate_mul", "add_concat", "relu2", "moe_route", "moe_align", "moe_gemm", "moe_combine"]
+             "conv_state_update", "gate_mul", "add_concat", "relu2", "moe_route", "moe_align", "moe_gemm", "moe_combine",
+             "moe_gather", "gemm_tc_grouped"]
 
 
 class PartTimer:

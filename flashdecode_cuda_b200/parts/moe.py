@@ -10,7 +10,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import FeedForward, Runtime
-from .linear import matmul
+from .linear import fused_prompt_gemm, matmul
 
 # Up to this many tokens the routing kernel makes the router's logits itself (one launch, a CTA per token, each reading
 # the whole router matrix); above it they come from a matrix product.
@@ -101,8 +101,11 @@ class RoutedExperts(FeedForward):
         shared = None
         if self.s_up is not None:
             h = ws.get("moe_shared_h", (T, self.shared_ff), x.dtype)
-            matmul(x, self.s_up, None, h, status=self.rt.status)
-            K.relu2(h, h)
+            if x.dtype == torch.bfloat16 and fused_prompt_gemm(T, self.shared_ff, H):
+                K.gemm_tc(x, self.s_up, None, h, status=self.rt.status, relu2=True)      # prompts: the activation in the epilogue
+            else:
+                matmul(x, self.s_up, None, h, status=self.rt.status)
+                K.relu2(h, h)
             shared = ws.get("moe_shared_out", (T, H), x.dtype)
             matmul(h, self.s_down, None, shared, target_ctas=4 * self.rt.sm_count, status=self.rt.status)
         y = pair_pos = None
@@ -115,7 +118,7 @@ class RoutedExperts(FeedForward):
             n_tiles = ws.get("moe_n_tiles", (1,), torch.int32)
             K.moe_align(ids, self.E, pair_pos, sorted_pair, tile_expert, n_tiles, mt)
             act = ws.get("moe_act", (cap, self.ff), x.dtype)
-            y = ws.get("moe_y", (cap, H), torch.float32)
+            y = ws.get("moe_y", (cap, H), x.dtype)
             if (mt == 128 and GROUPED_GEMM == "auto" and K.gemm_tc_grouped_supported(self.ff, H)
                     and K.gemm_tc_grouped_supported(H, self.ff)):
                 # prompts: the grouped rows as one matrix, then both products on the tcgen05 tensor cores

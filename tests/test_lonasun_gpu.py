@@ -231,7 +231,7 @@ def test_routed_experts(dtype, E, n_id, top, H, ff, T):
         w_down = torch.stack([W[f"m.mlp.e{e}.down"] for e in range(E)]).to(DEV)
         act = torch.zeros(cap, ff, dtype=dt, device=DEV)
         K.moe_gemm(x, w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
-        y = torch.zeros(cap, H, device=DEV)
+        y = torch.zeros(cap, H, dtype=dt, device=DEV)
         K.moe_gemm(act, w_down, y, True, sorted_pair, tile_expert, n_tiles, top, mt)
     out = torch.zeros(T, H, dtype=dt, device=DEV)
     K.moe_combine(y, x, None, ids, wts, pair_pos, out, E)
@@ -259,7 +259,7 @@ def test_grouped_products_on_tcgen05_equal_the_plain_experts(E, H, ff, T, top):
     K.moe_align(ids.to(DEV), E, pair_pos, sorted_pair, tile_expert, n_tiles, mt)
     xs = torch.full((cap, H), 7.0, dtype=dt, device=DEV)
     act = torch.full((cap, ff), 7.0, dtype=dt, device=DEV)
-    y = torch.full((cap, H), 7.0, device=DEV)
+    y = torch.full((cap, H), 7.0, dtype=dt, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     K.moe_gather(x.to(DEV), xs, sorted_pair, n_tiles, top, mt)
     K.gemm_tc_grouped(xs, w_up.to(DEV), act, True, tile_expert, n_tiles, status)
