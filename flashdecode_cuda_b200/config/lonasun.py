@@ -5,12 +5,14 @@ constant per layer: ``layers[i]`` holds ``type`` (which mixer), ``mixer`` (its
 sizes and constants) and ``mlp`` (the feed-forward, or null); ``loop`` names a
 span of layers that runs several times with the same weights; ``norm.eps``,
 ``vocab`` and ``width`` are global.  Nothing has a default: a key the design
-needs and the file lacks is an error, and so is a key this reader does not know.
+needs and the file lacks is an error.  A key this reader does not know changes
+nothing it computes; it is kept in ``unknown_keys`` and named in one warning.
 """
 
 from __future__ import annotations
 
 import copy
+import warnings
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
@@ -23,10 +25,13 @@ def _need(d: Dict[str, Any], key: str, where: str):
     return d[key]
 
 
+_UNKNOWN: List[str] = []       # filled while a configuration is read
+
+
 def _only(d: Dict[str, Any], known, where: str) -> None:
-    extra = sorted(set(d) - set(known))
-    if extra:
-        raise ConfigError(f"config.json: {where} has keys this design does not define: {extra}")
+    if not isinstance(d, dict):
+        raise ConfigError(f"config.json: {where} must be an object")
+    _UNKNOWN.extend(f"{where}.{k}" for k in sorted(set(d) - set(known)))
 
 
 @dataclass
@@ -117,12 +122,13 @@ class LonasunConfig:
     loop_times: int = 0              # 0: no loop, every layer runs once
     eos_token_id: Optional[Any] = None
     architecture: str = "Lonasun"
-    extra: Dict[str, Any] = field(default_factory=dict)
+    unknown_keys: List[str] = field(default_factory=list)     # keys of config.json this design does not define
 
     MIXERS = {"attention": ChunkedConvAttentionConfig}
 
     @classmethod
     def from_dict(cls, cfg: Dict[str, Any]) -> "LonasunConfig":
+        _UNKNOWN.clear()
         _only(cfg, ("architecture", "architectures", "layers", "loop", "norm", "vocab", "width", "eos_token_id"),
               "the top level")
         layers = []
@@ -151,6 +157,9 @@ class LonasunConfig:
                   loop_start=start, loop_stop=stop, loop_times=times, eos_token_id=cfg.get("eos_token_id"))
         if out.vocab <= 0 or out.width <= 0 or not out.norm_eps > 0:
             raise ConfigError("config.json: vocab, width and norm.eps must be positive")
+        out.unknown_keys = list(_UNKNOWN)
+        if out.unknown_keys:
+            warnings.warn(f"config.json has keys the Lonasun design does not define (ignored): {out.unknown_keys}")
         return out
 
     def layer_runs(self) -> List[tuple]:

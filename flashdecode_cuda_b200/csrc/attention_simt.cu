@@ -1,5 +1,5 @@
 // Causal grouped-query attention over the paged KV cache on the CUDA cores,
-// for any head size that is a multiple of 16 (up to 256; values may have a
+// for any head size that is a multiple of 8 (up to 256; values may have a
 // size of their own), any group size up to 64, any block size, an optional
 // sliding window or chunked visibility (keys of the query's own chunk of
 // `chunk` positions only, chunks counted from the start of the sequence),
@@ -361,8 +361,8 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
-    FD_REQUIRE(d % 16 == 0 && d >= 16 && d <= 256, -2, "attention: head size %d must be a multiple of 16 in [16, 256]", d);
-    FD_REQUIRE(dv % 16 == 0 && dv >= 16 && dv <= 256, -2, "attention: value head size %d must be a multiple of 16 in [16, 256]", dv);
+    FD_REQUIRE(d % 8 == 0 && d >= 8 && d <= 256, -2, "attention: head size %d must be a multiple of 8 in [8, 256]", d);
+    FD_REQUIRE(dv % 8 == 0 && dv >= 8 && dv <= 256, -2, "attention: value head size %d must be a multiple of 8 in [8, 256]", dv);
     FD_REQUIRE(chunk >= 0 && window >= 0, -2, "attention: chunk %d and window %d must not be negative", chunk, window);
     FD_REQUIRE(G <= RMAX, -2, "attention: group size %d exceeds %d", G, RMAX);
     FD_REQUIRE(block_size > 0, -2, "attention: block size %d", block_size);

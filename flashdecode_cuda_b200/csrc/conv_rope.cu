@@ -24,110 +24,152 @@
 namespace fd {
 
 constexpr int CONV_MAX_TAPS = 8;      // more taps than this take the loop that loads one value at a time
+constexpr int CONV_TPC = 8;           // tokens a CTA of a prompt step takes
 
-// A CTA takes one head (of q, k or v) of `tpc` consecutive tokens of the step, one after another; a thread one channel
-// of it: it loads the values its taps see (independent loads, issued together), convolves, leaves the result in shared
-// memory for its rotation partner, rotates and stores.  In a step of single tokens the same thread also moves the
-// channel's state on: it holds the old state in registers already.  (One token per CTA in a prompt step of 2,048
-// tokens meant 49,000 CTAs of a few loads each, 70 us of which most was their scheduling.)
+// A CTA takes one head (of q, k or v) of up to `tpc` <= CONV_TPC consecutive tokens of the step; a thread one channel
+// of it.  First the thread convolves its channel for all of the CTA's tokens: the values its taps see are independent
+// loads, issued together (a token's earlier values come from the step's own rows or, before the row's first new token,
+// from the sequence's state).  The results go through shared memory to the rotation partners; after ONE barrier the
+// thread rotates and stores q to its buffer, k and v to the paged pools.  In a step of single tokens the same thread also
+// moves the channel's state on: it holds the old state in registers already.  (One token per CTA and barrier in a prompt
+// step of 2,048 tokens took 79 us under ncu, nearly all of it waiting: 2 % of the DRAM rate.)
 template <typename T>
-__global__ void conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
-                                        float* __restrict__ state, T* __restrict__ q_out,
-                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                        int table_len, int rot, const int* __restrict__ tok_row,
-                                        const int* __restrict__ tok_pos, const int* __restrict__ row_slot,
-                                        const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
-                                        T* __restrict__ k_pool, T* __restrict__ v_pool,
-                                        const int* __restrict__ block_table, int max_blocks, int num_blocks,
-                                        int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
-                                        int update_state, int* status, int n_tok, int tpc) {
-    extern __shared__ float y_s[];                 // the head's convolved channels
+__global__ void __launch_bounds__(256)
+conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                        float* __restrict__ state, T* __restrict__ q_out,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                        int table_len, int rot, const int* __restrict__ tok_row,
+                        const int* __restrict__ tok_pos, const int* __restrict__ row_slot,
+                        const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
+                        T* __restrict__ k_pool, T* __restrict__ v_pool,
+                        const int* __restrict__ block_table, int max_blocks, int num_blocks,
+                        int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
+                        int update_state, int* status, int n_tok, int tpc) {
+    extern __shared__ float y_s[];                 // [tpc][width]: the head's convolved channels of every token
     const int hu = blockIdx.y;                     // head unit: q heads, then k heads, then v heads
-  for (int t = blockIdx.x * tpc; t < min(n_tok, (int)(blockIdx.x + 1) * tpc); ++t) {
-    __syncthreads();                               // the token before is done with y_s
-    const int r = tok_row[t];
-    const int slot = row_slot[r];
-    if (slot < 0) continue;                        // padding row
+    const int t0 = blockIdx.x * tpc;
+    const int nt = min(tpc, n_tok - t0);
     const int C = (n_q + n_kv) * d + n_kv * dv;
     const bool is_v = hu >= n_q + n_kv;
     const int width = is_v ? dv : d;
     const int c0 = is_v ? (n_q + n_kv) * d + (hu - n_q - n_kv) * dv : hu * d;     // the head's first channel
     const int j = threadIdx.x;
-    const int q_start = row_q_start[r];
-    const int i = t - q_start;                     // index of the token among the row's new tokens
-    const int pos = tok_pos[t];
     const int hist = taps - 1;
-    float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
-    const bool move_state = update_state && st != nullptr && row_q_len[r] == 1;
+    const bool active = j < width;
+    const int c = c0 + (active ? j : 0);
 
-    float y = 0.f;
-    if (j < width) {
-        const int c = c0 + j;
-        if (taps <= CONV_MAX_TAPS) {
-            float u[CONV_MAX_TAPS], wk[CONV_MAX_TAPS];
+    float y[CONV_TPC];
+    int slot_of[CONV_TPC];
+    if (taps <= CONV_MAX_TAPS) {
+        float wk[CONV_MAX_TAPS];
+#pragma unroll
+        for (int k = 0; k < CONV_MAX_TAPS; ++k) wk[k] = (active && k < taps) ? conv_w[(size_t)c * taps + k] : 0.f;
+#pragma unroll
+        for (int tt = 0; tt < CONV_TPC; ++tt) {
+            y[tt] = 0.f;
+            slot_of[tt] = -1;
+            if (tt >= nt) continue;
+            const int t = t0 + tt;
+            const int r = tok_row[t];
+            const int slot = row_slot[r];
+            slot_of[tt] = slot;
+            if (slot < 0 || !active) continue;     // padding row
+            const int q_start = row_q_start[r];
+            const int i = t - q_start;             // index of the token among the row's new tokens
+            float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
+            float u[CONV_MAX_TAPS];
 #pragma unroll
             for (int k = 0; k < CONV_MAX_TAPS; ++k) {
-                u[k] = 0.f; wk[k] = 0.f;
+                u[k] = 0.f;
                 if (k < taps) {
                     const int m = i - hist + k;    // index among the row's new tokens of the value this tap sees
-                    wk[k] = conv_w[(size_t)c * taps + k];
                     u[k] = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
                                   : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
                 }
             }
+            float acc = 0.f;
 #pragma unroll
             for (int k = 0; k < CONV_MAX_TAPS; ++k)
-                if (k < taps) y = fmaf(wk[k], u[k], y);
-            if (move_state) {                      // i == 0: u[0 .. hist-1] is the old state, u[hist] this token's value
+                if (k < taps) acc = fmaf(wk[k], u[k], acc);
+            y[tt] = acc;
+            if (update_state && st != nullptr && row_q_len[r] == 1) {
+                // i == 0: u[0 .. hist-1] is the old state, u[hist] this token's value
 #pragma unroll
                 for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
                     if (k < hist) st[(size_t)k * C + c] = u[k + 1];
             }
-        } else {
+        }
+    } else {
+        for (int tt = 0; tt < CONV_TPC; ++tt) {
+            y[tt] = 0.f;
+            slot_of[tt] = -1;
+            if (tt >= nt) continue;
+            const int t = t0 + tt;
+            const int r = tok_row[t];
+            const int slot = row_slot[r];
+            slot_of[tt] = slot;
+            if (slot < 0 || !active) continue;
+            const int q_start = row_q_start[r];
+            const int i = t - q_start;
+            float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
+            float acc = 0.f;
             for (int k = 0; k < taps; ++k) {
                 const int m = i - hist + k;
                 const float u = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
                                        : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
-                y = fmaf(conv_w[(size_t)c * taps + k], u, y);
+                acc = fmaf(conv_w[(size_t)c * taps + k], u, acc);
             }
-            if (move_state) {
+            y[tt] = acc;
+            if (update_state && st != nullptr && row_q_len[r] == 1) {
                 for (int s = 0; s + 1 < hist; ++s) st[(size_t)s * C + c] = st[(size_t)(s + 1) * C + c];
                 st[(size_t)(hist - 1) * C + c] = to_float(proj[(size_t)t * ld + c]);
             }
         }
-        y_s[j] = y;
+    }
+    if (active) {
+#pragma unroll
+        for (int tt = 0; tt < CONV_TPC; ++tt)
+            if (tt < nt) y_s[tt * width + j] = y[tt];
     }
     __syncthreads();
-    if (j >= width) continue;
+    if (!active) return;
 
     const int half = rot >> 1;
-    const bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
-    if (!pos_ok && j == 0 && hu == 0) set_status(status, STATUS_BAD_POSITION);
-    if (!is_v && j < rot && pos_ok) {              // q and k heads: rotate the leading `rot` dimensions
-        const float* cs = cos_t + (size_t)pos * half;
-        const float* sn = sin_t + (size_t)pos * half;
-        if (j < half) y = y * cs[j] - y_s[j + half] * sn[j];
-        else y = y * cs[j - half] + y_s[j - half] * sn[j - half];
+#pragma unroll
+    for (int tt = 0; tt < CONV_TPC; ++tt) {
+        if (tt >= nt) continue;
+        const int slot = slot_of[tt];
+        if (slot < 0) continue;
+        const int t = t0 + tt;
+        const int pos = tok_pos[t];
+        float v = y[tt];
+        const bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
+        if (!pos_ok && j == 0 && hu == 0) set_status(status, STATUS_BAD_POSITION);
+        if (!is_v && j < rot && pos_ok) {          // q and k heads: rotate the leading `rot` dimensions
+            const float* cs = cos_t + (size_t)pos * half;
+            const float* sn = sin_t + (size_t)pos * half;
+            if (j < half) v = v * cs[j] - y_s[tt * width + j + half] * sn[j];
+            else v = v * cs[j - half] + y_s[tt * width + j - half] * sn[j - half];
+        }
+        if (hu < n_q) {
+            q_out[(size_t)t * n_q * d + c0 + j] = from_float<T>(v);
+            continue;
+        }
+        if (!write_kv || pos < 0) continue;
+        const int col = pos / block_size;
+        const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
+        if (blk < 0 || blk >= num_blocks) {
+            if (j == 0) set_status(status, STATUS_BAD_BLOCK);
+            continue;
+        }
+        if (is_v) {
+            const int h = hu - n_q - n_kv;
+            v_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * dv + j] = from_float<T>(v);
+        } else {
+            const int h = hu - n_q;
+            k_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * d + j] = from_float<T>(v);
+        }
     }
-    if (hu < n_q) {
-        q_out[(size_t)t * n_q * d + c0 + j] = from_float<T>(y);
-        continue;
-    }
-    if (!write_kv || pos < 0) continue;
-    const int col = pos / block_size;
-    const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
-    if (blk < 0 || blk >= num_blocks) {
-        if (j == 0) set_status(status, STATUS_BAD_BLOCK);
-        continue;
-    }
-    if (is_v) {
-        const int h = hu - n_q - n_kv;
-        v_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * dv + j] = from_float<T>(y);
-    } else {
-        const int h = hu - n_q;
-        k_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * d + j] = from_float<T>(y);
-    }
-  }
 }
 
 // state[slot][s] <- the value (taps - 1 - s) places before the end of the row after this step: one of the step's
@@ -216,10 +258,10 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
     const int C = (n_q + n_kv) * d + n_kv * dv;
     FD_REQUIRE(ld >= C, -2, "conv_rope_append: rows of %d columns cannot hold %d channels", ld, C);
     const int widest = d > dv ? d : dv;
-    FD_REQUIRE(widest <= 1024 && n_q + 2 * n_kv <= 65535, -2, "conv_rope_append: heads of %d channels (max 1024)", widest);
-    const size_t smem = (size_t)widest * sizeof(float);
+    FD_REQUIRE(widest <= 256 && n_q + 2 * n_kv <= 65535, -2, "conv_rope_append: heads of %d channels (max 256)", widest);
     const int threads = (widest + 31) / 32 * 32;
-    const int tpc = T > 64 ? 8 : 1;               // tokens a CTA takes, one after another
+    const int tpc = T > 64 ? CONV_TPC : 1;        // tokens a CTA takes
+    const size_t smem = (size_t)tpc * widest * sizeof(float);
     const dim3 grid((T + tpc - 1) / tpc, n_q + 2 * n_kv);
     if (dtype == 0) {
         auto k = conv_rope_append_kernel<float>;

@@ -41,9 +41,9 @@ class ConvGatedAttention(Mixer):
                  taps: int, scale: float, position=None, rot_dims: int = 0, chunk: Optional[int] = None,
                  window: Optional[int] = None, gate: bool = True):
         for what, n in (("head size", head_dim), ("value head size", v_head_dim)):
-            if n < 16 or n > 256 or n % 16 != 0:
-                raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take multiples of 16 "
-                                 f"from 16 to 256")
+            if n < 8 or n > 256 or n % 8 != 0:
+                raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take multiples of 8 "
+                                 f"from 8 to 256")
         if n_kv_heads < 1 or n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 64:
             raise ValueError(f"{prefix}: {n_heads} query heads for {n_kv_heads} key/value heads: the kernels take whole "
                              f"groups of up to 64 query heads per key/value head")

@@ -35,10 +35,11 @@ def test_config_errors_name_the_place():
     del bad["layers"][1]["mixer"]["vdim"]
     with pytest.raises(ConfigError, match=r"layers\[1\]\.mixer misses 'vdim'"):
         load_config(bad)
-    bad = copy.deepcopy(LONASUN["X"])
-    bad["layers"][0]["mixer"]["sink"] = 4
-    with pytest.raises(ConfigError, match="does not define"):
-        load_config(bad)
+    odd = copy.deepcopy(LONASUN["X"])
+    odd["layers"][0]["mixer"]["sink"] = 4
+    with pytest.warns(UserWarning, match="does not define"):
+        cfg = load_config(odd)
+    assert cfg.unknown_keys == ["layers[0].mixer.sink"] and cfg.to_dict() == LONASUN["X"]
     bad = copy.deepcopy(LONASUN["X"])
     bad["layers"][0]["type"] = "recurrent"
     with pytest.raises(ConfigError, match="mixers are"):

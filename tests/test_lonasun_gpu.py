@@ -53,7 +53,8 @@ def make_pools(n_blocks, n_kv, bs, d, dv, dtype):
 # ---------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("taps,rot,d,dv,cuts", [(3, 8, 16, 32, [5, 1, 1, 6]), (4, 16, 16, 16, [2, 2, 9]),
-                                                (1, 0, 32, 16, [7, 1]), (2, 32, 32, 48, [1, 1, 1, 10])])
+                                                (1, 0, 32, 16, [7, 1]), (2, 32, 32, 48, [1, 1, 1, 10]),
+                                                (9, 4, 8, 8, [3, 1, 1, 10, 1])])     # more taps than the kernel unrolls
 def test_convolution_rotation_and_append(dtype, taps, rot, d, dv, cuts):
     """Two sequences fed in portions (some of one token, some shorter than the taps): q, the cached keys and values
     and the carried state equal the plain convolution and rotation of the whole sequences."""
@@ -169,6 +170,7 @@ ATTN_CASES = [  # d, dv, G, n_kv, chunk, block size, length
     (128, 128, 1, 2, 100, 64, 330),    # head size 128: the widest prompt kernel; a chunk that is no multiple of anything
     (32, 48, 2, 2, 24, 8, 100),        # values wider than keys: the CUDA-core kernel
     (48, 16, 3, 1, 37, 4, 120),
+    (24, 40, 2, 2, 30, 16, 100),       # head sizes that are multiples of 8 only
 ]
 
 
