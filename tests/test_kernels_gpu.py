@@ -829,7 +829,7 @@ def test_attention_decode_tensor_cores_window_and_far_key(window, decode_form):
 
 def test_attention_refuses_what_it_cannot_do():
     with pytest.raises(K.KernelError, match="head size"):
-        run_attention("float32", 4, 2, 24, 4, ctx=[0], new=[3])
+        run_attention("float32", 4, 2, 20, 4, ctx=[0], new=[3])
     with pytest.raises(K.KernelError, match="multiple"):
         run_attention("float32", 5, 2, 32, 4, ctx=[0], new=[3])
 
