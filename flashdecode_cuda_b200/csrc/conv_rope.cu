@@ -26,15 +26,27 @@ namespace fd {
 constexpr int CONV_MAX_TAPS = 8;      // more taps than this take the loop that loads one value at a time
 constexpr int CONV_TPC = 8;           // tokens a CTA of a prompt step takes
 
-// A CTA takes one head (of q, k or v) of up to `tpc` <= CONV_TPC consecutive tokens of the step; a thread one channel
-// of it.  First the thread convolves its channel for all of the CTA's tokens: the values its taps see are independent
-// loads, issued together (a token's earlier values come from the step's own rows or, before the row's first new token,
-// from the sequence's state).  The results go through shared memory to the rotation partners; after ONE barrier the
-// thread rotates and stores q to its buffer, k and v to the paged pools.  In a step of single tokens the same thread also
-// moves the channel's state on: it holds the old state in registers already.  (One token per CTA and barrier in a prompt
-// step of 2,048 tokens took 79 us under ncu, nearly all of it waiting: 2 % of the DRAM rate.)
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// A CTA takes one head (of q, k or v) of up to `tpc` <= CONV_TPC consecutive tokens of the step; a thread two adjacent
+// channels of it (head sizes, the row length of proj and the channel count are even: 4-byte loads of bfloat16 pairs).
+// What the tokens need to know - row, slot, place in the row, position, cache block - is looked up once per CTA into
+// shared memory.  Then a thread convolves its channels for all of the CTA's tokens: the values its taps see are
+// independent loads, issued together (a token's earlier values come from the step's own rows or, before the row's first
+// new token, from the sequence's state).  The results go through shared memory to the rotation partners; after one
+// barrier the thread rotates and stores q to its buffer, k and v to the paged pools.  In a step of single tokens the
+// same thread also moves its channels' state on: it holds the old state in registers already.  (A thread per channel
+// with its own lookups, 2-byte loads and a division by the page size per token took 75-79 us for a prompt step of
+// 2,048 tokens, bound by instruction issue: 2 % of the DRAM rate under ncu.)
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
                         float* __restrict__ state, T* __restrict__ q_out,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -46,90 +58,108 @@ conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restr
                         int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
                         int update_state, int* status, int n_tok, int tpc) {
     extern __shared__ float y_s[];                 // [tpc][width]: the head's convolved channels of every token
+    __shared__ int m_slot[CONV_TPC], m_start[CONV_TPC], m_i[CONV_TPC], m_pos[CONV_TPC], m_move[CONV_TPC];
+    __shared__ long long m_dst[CONV_TPC];          // element offset of the token's key or value row of this head, or -1
     const int hu = blockIdx.y;                     // head unit: q heads, then k heads, then v heads
     const int t0 = blockIdx.x * tpc;
     const int nt = min(tpc, n_tok - t0);
     const int C = (n_q + n_kv) * d + n_kv * dv;
-    const bool is_v = hu >= n_q + n_kv;
+    const bool is_q = hu < n_q, is_v = hu >= n_q + n_kv;
     const int width = is_v ? dv : d;
     const int c0 = is_v ? (n_q + n_kv) * d + (hu - n_q - n_kv) * dv : hu * d;     // the head's first channel
-    const int j = threadIdx.x;
     const int hist = taps - 1;
+
+    if (threadIdx.x < nt) {
+        const int tt = threadIdx.x, t = t0 + tt;
+        const int r = tok_row[t];
+        const int slot = row_slot[r];
+        const int q_start = row_q_start[r];
+        const int pos = tok_pos[t];
+        m_slot[tt] = slot; m_start[tt] = q_start; m_i[tt] = t - q_start; m_pos[tt] = pos;
+        m_move[tt] = update_state && state != nullptr && slot >= 0 && row_q_len[r] == 1;
+        long long dst = -1;
+        if (slot >= 0) {
+            if (rot > 0 && (pos < 0 || pos >= table_len) && hu == 0) set_status(status, STATUS_BAD_POSITION);
+            if (!is_q && write_kv && pos >= 0) {
+                const int col = pos / block_size;
+                const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
+                if (blk < 0 || blk >= num_blocks) set_status(status, STATUS_BAD_BLOCK);
+                else dst = (((long long)blk * n_kv + (is_v ? hu - n_q - n_kv : hu - n_q)) * block_size + (pos - col * block_size)) * width;
+            }
+        }
+        m_dst[tt] = dst;
+    }
+    __syncthreads();
+
+    const int j = threadIdx.x * 2;                 // this thread's channels of the head: j, j + 1
     const bool active = j < width;
     const int c = c0 + (active ? j : 0);
-
-    float y[CONV_TPC];
-    int slot_of[CONV_TPC];
+    float y0[CONV_TPC], y1[CONV_TPC];
     if (taps <= CONV_MAX_TAPS) {
-        float wk[CONV_MAX_TAPS];
+        float w0[CONV_MAX_TAPS], w1[CONV_MAX_TAPS];
 #pragma unroll
-        for (int k = 0; k < CONV_MAX_TAPS; ++k) wk[k] = (active && k < taps) ? conv_w[(size_t)c * taps + k] : 0.f;
+        for (int k = 0; k < CONV_MAX_TAPS; ++k) {
+            w0[k] = (active && k < taps) ? conv_w[(size_t)c * taps + k] : 0.f;
+            w1[k] = (active && k < taps) ? conv_w[(size_t)(c + 1) * taps + k] : 0.f;
+        }
 #pragma unroll
         for (int tt = 0; tt < CONV_TPC; ++tt) {
-            y[tt] = 0.f;
-            slot_of[tt] = -1;
-            if (tt >= nt) continue;
-            const int t = t0 + tt;
-            const int r = tok_row[t];
-            const int slot = row_slot[r];
-            slot_of[tt] = slot;
-            if (slot < 0 || !active) continue;     // padding row
-            const int q_start = row_q_start[r];
-            const int i = t - q_start;             // index of the token among the row's new tokens
-            float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
-            float u[CONV_MAX_TAPS];
+            y0[tt] = y1[tt] = 0.f;
+            if (tt >= nt || !active) continue;
+            const int slot = m_slot[tt];
+            if (slot < 0) continue;                // padding row
+            const int q_start = m_start[tt], i = m_i[tt];
+            float* st = state != nullptr ? state + (size_t)slot * hist * C + c : nullptr;
+            float2 u[CONV_MAX_TAPS];
 #pragma unroll
             for (int k = 0; k < CONV_MAX_TAPS; ++k) {
-                u[k] = 0.f;
+                u[k] = make_float2(0.f, 0.f);
                 if (k < taps) {
                     const int m = i - hist + k;    // index among the row's new tokens of the value this tap sees
-                    u[k] = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
-                                  : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
+                    if (m >= 0) u[k] = load2(proj + (size_t)(q_start + m) * ld + c);
+                    else if (st != nullptr) u[k] = *reinterpret_cast<const float2*>(st + (size_t)(hist + m) * C);
                 }
             }
-            float acc = 0.f;
+            float a0 = 0.f, a1 = 0.f;
 #pragma unroll
             for (int k = 0; k < CONV_MAX_TAPS; ++k)
-                if (k < taps) acc = fmaf(wk[k], u[k], acc);
-            y[tt] = acc;
-            if (update_state && st != nullptr && row_q_len[r] == 1) {
-                // i == 0: u[0 .. hist-1] is the old state, u[hist] this token's value
+                if (k < taps) { a0 = fmaf(w0[k], u[k].x, a0); a1 = fmaf(w1[k], u[k].y, a1); }
+            y0[tt] = a0; y1[tt] = a1;
+            if (m_move[tt]) {                      // i == 0: u[0 .. hist-1] is the old state, u[hist] this token's value
 #pragma unroll
                 for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
-                    if (k < hist) st[(size_t)k * C + c] = u[k + 1];
+                    if (k < hist) *reinterpret_cast<float2*>(st + (size_t)k * C) = u[k + 1];
             }
         }
     } else {
         for (int tt = 0; tt < CONV_TPC; ++tt) {
-            y[tt] = 0.f;
-            slot_of[tt] = -1;
-            if (tt >= nt) continue;
-            const int t = t0 + tt;
-            const int r = tok_row[t];
-            const int slot = row_slot[r];
-            slot_of[tt] = slot;
-            if (slot < 0 || !active) continue;
-            const int q_start = row_q_start[r];
-            const int i = t - q_start;
-            float* st = state != nullptr ? state + (size_t)slot * hist * C : nullptr;
-            float acc = 0.f;
+            y0[tt] = y1[tt] = 0.f;
+            if (tt >= nt || !active) continue;
+            const int slot = m_slot[tt];
+            if (slot < 0) continue;
+            const int q_start = m_start[tt], i = m_i[tt];
+            float* st = state != nullptr ? state + (size_t)slot * hist * C + c : nullptr;
+            float a0 = 0.f, a1 = 0.f;
             for (int k = 0; k < taps; ++k) {
                 const int m = i - hist + k;
-                const float u = m >= 0 ? to_float(proj[(size_t)(q_start + m) * ld + c])
-                                       : (st != nullptr ? st[(size_t)(hist + m) * C + c] : 0.f);
-                acc = fmaf(conv_w[(size_t)c * taps + k], u, acc);
+                float2 u = make_float2(0.f, 0.f);
+                if (m >= 0) u = load2(proj + (size_t)(q_start + m) * ld + c);
+                else if (st != nullptr) u = *reinterpret_cast<const float2*>(st + (size_t)(hist + m) * C);
+                a0 = fmaf(conv_w[(size_t)c * taps + k], u.x, a0);
+                a1 = fmaf(conv_w[(size_t)(c + 1) * taps + k], u.y, a1);
             }
-            y[tt] = acc;
-            if (update_state && st != nullptr && row_q_len[r] == 1) {
-                for (int s = 0; s + 1 < hist; ++s) st[(size_t)s * C + c] = st[(size_t)(s + 1) * C + c];
-                st[(size_t)(hist - 1) * C + c] = to_float(proj[(size_t)t * ld + c]);
+            y0[tt] = a0; y1[tt] = a1;
+            if (m_move[tt]) {
+                for (int s = 0; s + 1 < hist; ++s)
+                    *reinterpret_cast<float2*>(st + (size_t)s * C) = *reinterpret_cast<const float2*>(st + (size_t)(s + 1) * C);
+                *reinterpret_cast<float2*>(st + (size_t)(hist - 1) * C) = load2(proj + (size_t)(t0 + tt) * ld + c);
             }
         }
     }
     if (active) {
 #pragma unroll
         for (int tt = 0; tt < CONV_TPC; ++tt)
-            if (tt < nt) y_s[tt * width + j] = y[tt];
+            if (tt < nt) { y_s[tt * width + j] = y0[tt]; y_s[tt * width + j + 1] = y1[tt]; }
     }
     __syncthreads();
     if (!active) return;
@@ -137,37 +167,24 @@ conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restr
     const int half = rot >> 1;
 #pragma unroll
     for (int tt = 0; tt < CONV_TPC; ++tt) {
-        if (tt >= nt) continue;
-        const int slot = slot_of[tt];
-        if (slot < 0) continue;
-        const int t = t0 + tt;
-        const int pos = tok_pos[t];
-        float v = y[tt];
-        const bool pos_ok = pos >= 0 && (rot == 0 || pos < table_len);
-        if (!pos_ok && j == 0 && hu == 0) set_status(status, STATUS_BAD_POSITION);
-        if (!is_v && j < rot && pos_ok) {          // q and k heads: rotate the leading `rot` dimensions
+        if (tt >= nt || m_slot[tt] < 0) continue;
+        const int pos = m_pos[tt];
+        float v[2] = {y0[tt], y1[tt]};
+        if (!is_v && j < rot && pos >= 0 && pos < table_len) {      // q and k heads: rotate the leading `rot` dimensions
             const float* cs = cos_t + (size_t)pos * half;
             const float* sn = sin_t + (size_t)pos * half;
-            if (j < half) v = v * cs[j] - y_s[tt * width + j + half] * sn[j];
-            else v = v * cs[j - half] + y_s[tt * width + j - half] * sn[j - half];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int je = j + e;
+                if (je >= rot) continue;
+                if (je < half) v[e] = v[e] * cs[je] - y_s[tt * width + je + half] * sn[je];
+                else v[e] = v[e] * cs[je - half] + y_s[tt * width + je - half] * sn[je - half];
+            }
         }
-        if (hu < n_q) {
-            q_out[(size_t)t * n_q * d + c0 + j] = from_float<T>(v);
-            continue;
-        }
-        if (!write_kv || pos < 0) continue;
-        const int col = pos / block_size;
-        const int blk = col < max_blocks ? block_table[(size_t)slot * max_blocks + col] : -1;
-        if (blk < 0 || blk >= num_blocks) {
-            if (j == 0) set_status(status, STATUS_BAD_BLOCK);
-            continue;
-        }
-        if (is_v) {
-            const int h = hu - n_q - n_kv;
-            v_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * dv + j] = from_float<T>(v);
-        } else {
-            const int h = hu - n_q;
-            k_pool[(((size_t)blk * n_kv + h) * block_size + (pos % block_size)) * d + j] = from_float<T>(v);
+        if (is_q) {
+            store2(q_out + (size_t)(t0 + tt) * n_q * d + c0 + j, v[0], v[1]);
+        } else if (m_dst[tt] >= 0) {
+            store2((is_v ? v_pool : k_pool) + m_dst[tt] + j, v[0], v[1]);
         }
     }
 }
@@ -259,7 +276,10 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
     FD_REQUIRE(ld >= C, -2, "conv_rope_append: rows of %d columns cannot hold %d channels", ld, C);
     const int widest = d > dv ? d : dv;
     FD_REQUIRE(widest <= 256 && n_q + 2 * n_kv <= 65535, -2, "conv_rope_append: heads of %d channels (max 256)", widest);
-    const int threads = (widest + 31) / 32 * 32;
+    FD_REQUIRE(d % 2 == 0 && dv % 2 == 0 && ld % 2 == 0 && (uintptr_t)proj % 4 == 0 && (uintptr_t)state % 8 == 0 &&
+               (uintptr_t)q_out % 4 == 0 && (uintptr_t)k_pool % 4 == 0 && (uintptr_t)v_pool % 4 == 0, -2,
+               "conv_rope_append: head sizes (%d, %d) and rows of proj (%d) must be even, buffers aligned for pairs", d, dv, ld);
+    const int threads = (widest / 2 + 31) / 32 * 32;
     const int tpc = T > 64 ? CONV_TPC : 1;        // tokens a CTA takes
     const size_t smem = (size_t)tpc * widest * sizeof(float);
     const dim3 grid((T + tpc - 1) / tpc, n_q + 2 * n_kv);

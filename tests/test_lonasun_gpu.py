@@ -64,7 +64,7 @@ def test_convolution_rotation_and_append(dtype, taps, rot, d, dv, cuts):
     C = (n_q + n_kv) * d + n_kv * dv
     S = sum(cuts)
     lens = [S, S - 3]
-    u = [torch.randn(n, C + 5).to(dt) for n in lens]                 # five more columns that the kernel must leave alone
+    u = [torch.randn(n, C + 6).to(dt) for n in lens]                 # six more columns that the kernel must leave alone
     w = torch.randn(C, taps) * 0.5
     base = 100.0
     k_pool, v_pool = make_pools(16, n_kv, bs, d, dv, dt)
