@@ -53,6 +53,40 @@ LONASUN: Dict[str, dict] = {
 }
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: widths that are no power of two, head sizes that are multiples of 8 only, value
+    heads of another size than key heads, one to five taps, nothing to everything rotated, chunks from one position to
+    longer than any test sequence, routers with and without identity and shared experts, layers without a feed-forward,
+    layers that differ from one another, and loops anywhere in the stack."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([48, 72, 96, 128, 200, 256])
+    n_layers = rng.randint(1, 4)
+
+    def mixer():
+        kv, g = rng.choice([1, 2, 3]), rng.choice([1, 2, 4])
+        dim = rng.choice([8, 16, 24, 32, 40, 64, 128])
+        vdim = rng.choice([dim, dim, 8, 16, 48, 64])
+        rot = min(dim, rng.choice([0, 2, 4, 8, dim]))
+        return _mixer(kv * g, kv, dim, vdim, rng.choice([1, 2, 3, 4, 5]), rot - rot % 2, rng.choice([100.0, 10000.0, 250000.0]),
+                      rng.choice([0.1, 0.125, 0.3]), rng.choice([1, 3, 16, 17, 50, 64, 100, 1000]))
+
+    def mlp():
+        if rng.random() < 0.15:
+            return None
+        E, n_id = rng.choice([1, 2, 3, 8, 16]), rng.choice([0, 0, 1, 4])
+        return _moe(E, n_id, rng.randint(1, min(E + n_id, 5)), rng.choice([8, 24, 40, 96, 100]),
+                    rng.choice([None, 16, 56, 128]))
+    same = rng.random() < 0.5
+    m0, f0 = mixer(), mlp()
+    cfg = {"architecture": "Lonasun", "vocab": rng.choice([50, 333, 1000]), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])},
+           "layers": [_layer(m0 if same else mixer(), f0 if same else mlp()) for _ in range(n_layers)]}
+    if rng.random() < 0.7:
+        a = rng.randint(0, n_layers - 1)
+        cfg["loop"] = {"start": a, "stop": rng.randint(a + 1, n_layers), "times": rng.randint(1, 3)}
+    return cfg
+
+
 def write_folder(tmp: Path, name: str, seed: int = 0, fixed_choice: bool = False) -> Path:
     """A model folder with random weights.  ``fixed_choice``: the corrections of every router are set two apart, so
     they alone decide which experts are chosen (the same ones for every token of a layer), while the weights of the

@@ -14,7 +14,7 @@ import torch
 import flashdecode_cuda_b200 as fd
 from flashdecode_cuda_b200 import kernels as K
 from helpers import prompts_for, rel_err
-from lonasun_helpers import LONASUN, oracle_logits, plain_greedy, write_folder
+from lonasun_helpers import LONASUN, oracle_logits, plain_greedy, random_config, raw_config, weights_of, write_folder
 from plain import lonasun_plain as P
 
 pytestmark = pytest.mark.gpu
@@ -332,7 +332,6 @@ def test_every_layer_run_in_float32(engines, folders):
         eng = engines[(name, "float32")]
         (p,) = prompts_for(_vocab(name), [45], seed=2)
         trace = []
-        from lonasun_helpers import raw_config, weights_of
         P.forward(raw_config(folders[name]), weights_of(folders[name]), p, trace=trace)
         cache = eng.model.new_cache(max_tokens=64)
         slot = cache.admit()
@@ -439,6 +438,34 @@ def test_batch_neighbours_change_no_bit_in_float32(engines):
         b = eng.model.step(cache, slots, [[p[-2]] for p in reqs], "last").clone()
         for i in range(len(reqs)):
             assert torch.equal(a[i], alone[i][0][0]) and torch.equal(b[i], alone[i][1][0]), f"{name}: request {i}"
+
+
+@pytest.mark.parametrize("seed", range(100, 110))
+def test_configurations_drawn_at_random_in_float32(tmp_path, seed):
+    """Sizes nobody chose: a whole prompt, then a batch of unequal prompts decoded together, against the plain model."""
+    cfg = random_config(seed)
+    folder = fd.write_random_model(tmp_path / "m", cfg, seed)
+    W = weights_of(folder)
+    reqs = prompts_for(cfg["vocab"], [1, 37, 131], seed=seed)
+    want = [P.forward(cfg, W, r) for r in reqs]
+    eng = fd.load(folder, device="cuda", dtype="float32")
+    cache = eng.model.new_cache(max_tokens=256, max_slots=4, slack_blocks=4, block_size=16)
+    s = cache.admit()
+    assert rel_err(eng.model.step(cache, [s], [reqs[2]], "all"), want[2]) < 5e-5, cfg
+    cache.release(s)
+    slots = [cache.admit() for _ in reqs]
+    heads = [1, 30, 120]
+    got = eng.model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads)], "last")
+    for i in range(3):
+        assert rel_err(got[i], want[i][heads[i] - 1]) < 5e-5, cfg
+    cache.release(slots[0])
+    for step in range(7):
+        live = [i for i in (1, 2) if heads[i] + step < len(reqs[i])]
+        got = eng.model.step(cache, [slots[i] for i in live], [[reqs[i][heads[i] + step]] for i in live], "last")
+        for j, i in enumerate(live):
+            assert rel_err(got[j], want[i][heads[i] + step]) < 5e-5, (cfg, i, step)
+    eng.model.check_status()
+    cache.check_invariants()
 
 
 @pytest.mark.parametrize("name", NAMES)
