@@ -43,30 +43,39 @@ class ChunkedConvAttentionConfig:
     vdim: int                 # per-head value size
     conv: int                 # taps of the short convolution on q, k and v
     rot_dims: int             # leading dimensions of each head that are rotated
-    rot_base: float
+    rot_base: Optional[float]  # None: the configuration has no 'rot' (nothing is rotated)
     scale: float
-    chunk: int                # keys are visible inside the query's chunk of this many positions
+    chunk: Optional[int]      # keys are visible inside the query's chunk of this many positions (None: all earlier keys)
 
     @classmethod
     def from_dict(cls, m: Dict[str, Any], where: str) -> "ChunkedConvAttentionConfig":
         _only(m, ("heads", "kv_heads", "dim", "vdim", "conv", "rot", "scale", "mask"), where)
-        rot, mask = _need(m, "rot", where), _need(m, "mask", where)
-        _only(rot, ("dims", "base"), f"{where}.rot")
-        _only(mask, ("size",), f"{where}.mask")
+        # a mixer whose configuration has no 'rot' rotates nothing, one without 'mask' sees every earlier key
+        rot, mask = m.get("rot"), m.get("mask")
+        if rot is not None:
+            _only(rot, ("dims", "base"), f"{where}.rot")
+        if mask is not None:
+            _only(mask, ("size",), f"{where}.mask")
+        rot_dims = 0 if rot is None else int(_need(rot, "dims", f"{where}.rot"))
         c = cls(heads=int(_need(m, "heads", where)), kv_heads=int(_need(m, "kv_heads", where)),
                 dim=int(_need(m, "dim", where)), vdim=int(_need(m, "vdim", where)), conv=int(_need(m, "conv", where)),
-                rot_dims=int(_need(rot, "dims", f"{where}.rot")), rot_base=float(_need(rot, "base", f"{where}.rot")),
-                scale=float(_need(m, "scale", where)), chunk=int(_need(mask, "size", f"{where}.mask")))
-        if min(c.heads, c.kv_heads, c.dim, c.vdim, c.conv, c.chunk) <= 0 or c.heads % c.kv_heads:
+                rot_dims=rot_dims, rot_base=None if rot is None else float(_need(rot, "base", f"{where}.rot")),
+                scale=float(_need(m, "scale", where)),
+                chunk=None if mask is None else int(_need(mask, "size", f"{where}.mask")))
+        if min(c.heads, c.kv_heads, c.dim, c.vdim, c.conv, 1 if c.chunk is None else c.chunk) <= 0 or c.heads % c.kv_heads:
             raise ConfigError(f"config.json: {where}: sizes must be positive and heads a multiple of kv_heads")
         if c.rot_dims < 0 or c.rot_dims % 2 or c.rot_dims > c.dim or (c.rot_dims and not c.rot_base > 0):
             raise ConfigError(f"config.json: {where}.rot: dims must be even and at most dim, base positive")
         return c
 
     def to_dict(self) -> Dict[str, Any]:
-        return {"conv": self.conv, "dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads,
-                "mask": {"size": self.chunk}, "rot": {"base": self.rot_base, "dims": self.rot_dims},
-                "scale": self.scale, "vdim": self.vdim}
+        d = {"conv": self.conv, "dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads,
+             "scale": self.scale, "vdim": self.vdim}
+        if self.rot_base is not None:
+            d["rot"] = {"base": self.rot_base, "dims": self.rot_dims}
+        if self.chunk is not None:
+            d["mask"] = {"size": self.chunk}
+        return d
 
 
 @dataclass

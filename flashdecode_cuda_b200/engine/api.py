@@ -177,7 +177,7 @@ def build_model(config, tensors: Dict[str, torch.Tensor], device="cuda", dtype=t
 
 def load(model: Union[str, Path], device="cuda", dtype=torch.bfloat16, seed: Optional[int] = None) -> Engine:
     """An engine for a model folder (``config.json`` + ``model.safetensors``);
-    the model class is chosen by ``config.json["architectures"]``.  With
+    the model class is chosen by ``config.json["architectures"]`` (or ``["architecture"]``).  With
     ``seed`` given, ``model`` may instead name a preset (or a folder with only a
     ``config.json``) and the weights are drawn at random from the seed."""
     dtype = as_dtype(dtype)

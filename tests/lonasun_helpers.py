@@ -68,8 +68,13 @@ def random_config(seed: int) -> dict:
         dim = rng.choice([8, 16, 24, 32, 40, 64, 128])
         vdim = rng.choice([dim, dim, 8, 16, 48, 64])
         rot = min(dim, rng.choice([0, 2, 4, 8, dim]))
-        return _mixer(kv * g, kv, dim, vdim, rng.choice([1, 2, 3, 4, 5]), rot - rot % 2, rng.choice([100.0, 10000.0, 250000.0]),
-                      rng.choice([0.1, 0.125, 0.3]), rng.choice([1, 3, 16, 17, 50, 64, 100, 1000]))
+        m = _mixer(kv * g, kv, dim, vdim, rng.choice([1, 2, 3, 4, 5]), rot - rot % 2, rng.choice([100.0, 10000.0, 250000.0]),
+                   rng.choice([0.1, 0.125, 0.3]), rng.choice([1, 3, 16, 17, 50, 64, 100, 1000]))
+        if rng.random() < 0.15:
+            del m["mask"]                              # every earlier key is visible
+        if rng.random() < 0.1:
+            del m["rot"]                               # nothing is rotated
+        return m
 
     def mlp():
         if rng.random() < 0.15:

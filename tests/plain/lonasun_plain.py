@@ -106,9 +106,12 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict
     k = short_conv(h @ W[f"{p}.mix.k"].to(dt).T, W[f"{p}.mix.k.conv"].to(dt))
     v = short_conv(h @ W[f"{p}.mix.v"].to(dt).T, W[f"{p}.mix.v.conv"].to(dt))
     pos = torch.arange(S)
-    q = partial_rotation(q.view(S, H, d), pos, m["rot"]["dims"], m["rot"]["base"])
-    k = partial_rotation(k.view(S, G, d), pos, m["rot"]["dims"], m["rot"]["base"])
-    att = (chunked_attention_fast if fast else chunked_attention)(q, k, v.view(S, G, dv), m["scale"], m["mask"]["size"])
+    q, k = q.view(S, H, d), k.view(S, G, d)
+    if m.get("rot"):                                   # no 'rot': nothing is rotated
+        q = partial_rotation(q, pos, m["rot"]["dims"], m["rot"]["base"])
+        k = partial_rotation(k, pos, m["rot"]["dims"], m["rot"]["base"])
+    size = m["mask"]["size"] if m.get("mask") else S   # no 'mask': one chunk holds the whole sequence
+    att = (chunked_attention_fast if fast else chunked_attention)(q, k, v.view(S, G, dv), m["scale"], size)
     gate = torch.sigmoid(h @ W[f"{p}.mix.g"].to(dt).T)
     return (att.reshape(S, H * dv) * gate) @ W[f"{p}.mix.o"].to(dt).T
 

@@ -54,6 +54,18 @@ def test_config_errors_name_the_place():
         load_config(bad)
 
 
+def test_a_mixer_without_mask_or_rotation_in_its_configuration():
+    plain = copy.deepcopy(LONASUN["Z"])
+    for layer in plain["layers"]:
+        del layer["mixer"]["mask"]
+    del plain["layers"][0]["mixer"]["rot"]
+    cfg = load_config(plain)
+    assert [L.mixer.chunk for L in cfg.layers] == [None] * 3 and cfg.layers[0].mixer.rot_dims == 0
+    m = Model.from_config(cfg, torch.float32, "cpu")
+    assert all(g.chunk is None for g in m.cache_groups())
+    assert "mask" not in cfg.to_dict()["layers"][1]["mixer"]
+
+
 def test_blueprint_declares_every_tensor_once_and_orders_the_runs():
     cfg = load_config(LONASUN["X"])
     m = Model.from_config(cfg, torch.float32, "cpu")
