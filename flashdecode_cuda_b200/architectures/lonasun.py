@@ -1,6 +1,6 @@
 """Lonasun as a blueprint of parts.
 
-A decoder of pre-norm layers (RMS norm with a weight stored around zero);
+A decoder of pre-norm layers (RMS norm whose gain is kept as an offset from one);
 every layer's mixer is attention with a short convolution on q, k and v, a
 partial rotation, chunked visibility and an output gate; its feed-forward is a
 mixture of relu^2 experts with identity experts and a shared expert, or absent.

@@ -26,7 +26,7 @@ class RMSNorm(Norm):
 
     def __init__(self, prefix: str, size: int, eps: float, unit_offset: bool = False, tensor: Optional[str] = None,
                  optional: bool = False):
-        """``unit_offset``: the stored weight lies around zero and the norm multiplies by 1 + weight (added in
+        """``unit_offset``: the checkpoint holds the gain's offset from one and the norm multiplies by 1 + weight (added in
         float32 when the weights are bound).  ``tensor``: the weight's full name where it is not
         ``<prefix>.weight``.  ``optional``: a checkpoint may lack the weight (a norm that never runs)."""
         self.name = tensor or f"{prefix}.weight"

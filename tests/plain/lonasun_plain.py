@@ -24,7 +24,7 @@ import torch
 
 
 def unit_offset_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """x / sqrt(mean(x^2) + eps) * (1 + w): the weight is stored around zero."""
+    """x / sqrt(mean(x^2) + eps) * (1 + w): the checkpoint holds the gain's offset from one."""
     ms = x.pow(2).mean(-1, keepdim=True)
     return x / torch.sqrt(ms + eps) * (1.0 + w)
 
