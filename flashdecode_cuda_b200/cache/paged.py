@@ -51,13 +51,16 @@ class KVGroupSpec:
     ``window`` positions.  ``chunk``: a query sees only the keys of its own
     chunk of that many positions (counted from the start of the sequence), so
     only blocks that reach into the chunk of the next query are kept.
-    ``v_head_dim``: size of a value head where it differs from a key head's."""
+    ``v_head_dim``: size of a value head where it differs from a key head's.
+    ``keys_only``: nothing but one vector per position and head is kept; it is read
+    as key and as value (``v_pool`` is ``k_pool``)."""
     n_layers: int
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     v_head_dim: Optional[int] = None
+    keys_only: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -98,7 +101,14 @@ class KVGroup:
         self.block_size = block_size
         self.max_blocks_per_seq = max_blocks_per_seq
         # [layer, k|v, block, kv head, token in block, dim]; keys and values of different head sizes: a pool each
-        if spec.value_dim == spec.head_dim:
+        if spec.keys_only:
+            if spec.value_dim != spec.head_dim:
+                raise ValueError("a group that keeps keys only reads them as values of the same size")
+            self.pool = None
+            self.keys = torch.zeros((spec.n_layers, num_blocks, spec.n_kv_heads, block_size, spec.head_dim),
+                                    dtype=dtype, device=device)
+            self.values = self.keys
+        elif spec.value_dim == spec.head_dim:
             self.pool = torch.zeros((spec.n_layers, 2, num_blocks, spec.n_kv_heads, block_size, spec.head_dim),
                                     dtype=dtype, device=device)
             self.keys, self.values = self.pool[:, 0], self.pool[:, 1]
@@ -162,7 +172,8 @@ class KVGroup:
 
     def bytes_per_token(self) -> int:
         s = self.spec
-        return s.n_layers * s.n_kv_heads * (s.head_dim + s.value_dim) * self.keys.element_size()
+        per_head = s.head_dim if s.keys_only else s.head_dim + s.value_dim
+        return s.n_layers * s.n_kv_heads * per_head * self.keys.element_size()
 
 
 class PagedCache:

@@ -13,6 +13,7 @@ from typing import Any, Dict, List, Union
 
 from ..registry import architecture
 from .lonasun import LonasunConfig
+from .nizazen import NizazenConfig
 from .qwen2 import ConfigError, Qwen2Config
 
 PRESET_DIR = Path(__file__).resolve().parent / "presets"
@@ -60,4 +61,4 @@ def load_config(source: Union[str, Path, Dict[str, Any]]):
     raise ConfigError(f"no config.json at {source!r} and no preset of that name; presets: {preset_names()}")
 
 
-__all__ = ["ConfigError", "Qwen2Config", "LonasunConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]
+__all__ = ["ConfigError", "Qwen2Config", "LonasunConfig", "NizazenConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]

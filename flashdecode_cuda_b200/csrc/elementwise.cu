@@ -183,11 +183,26 @@ add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, int n_parts, size_
     }
 }
 
+// The gated activations of the feed-forwards: what becomes of a gate value g and an up value u.
+//   GLU_SILU:    g * sigmoid(g) * u
+//   GLU_GELU:    0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u          (the tanh form of GELU)
+//   GLU_CLAMPED: g' * sigmoid(1.702 g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+constexpr int GLU_SILU = 0, GLU_GELU = 1, GLU_CLAMPED = 2;
+__device__ __forceinline__ float glu_value(int kind, float g, float u, float limit) {
+    if (kind == GLU_GELU) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    if (kind == GLU_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+    }
+    return g / (1.f + expf(-g)) * u;
+}
+
 // ---------------------------------------------------------------------------
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int kind, float limit) {
     size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; e < total; e += stride) {
@@ -195,7 +210,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
         const int i = (int)(e - m * I);
         const float g = to_float(gu[m * 2 * I + i]);
         const float u = to_float(gu[m * 2 * I + I + i]);
-        out[e] = from_float<T>(g / (1.f + expf(-g)) * u);
+        out[e] = from_float<T>(glu_value(kind, g, u, limit));
     }
 }
 
@@ -291,7 +306,7 @@ __global__ void rope_append_kernel(const TQ* __restrict__ qkv, int n_parts, size
 // out[m, i] = silu(g) * u where gate and up values of a row come in tiles of
 // 16 columns: 8 gate values, then the 8 up values of the same outputs.
 template <typename T>
-__global__ void silu_mul_tiled_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_tiled_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int kind, float limit) {
     size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; e < total; e += stride) {
@@ -300,8 +315,14 @@ __global__ void silu_mul_tiled_kernel(const T* __restrict__ gu, T* __restrict__ 
         const size_t base = m * 2 * I + (size_t)(i >> 3) * 16 + (i & 7);
         const float g = to_float(gu[base]);
         const float u = to_float(gu[base + 8]);
-        out[e] = from_float<T>(g / (1.f + expf(-g)) * u);
+        out[e] = from_float<T>(glu_value(kind, g, u, limit));
     }
+}
+
+// x <- cap * tanh(x / cap)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x)
+        x[e] = cap * tanhf(x[e] / cap);
 }
 
 }  // namespace fd
@@ -387,20 +408,37 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
 }
 
 // tiled == 0: gu = [gate (I columns) | up (I columns)]; tiled != 0: tiles of 8 gate + 8 up columns.
-extern "C" int fd_silu_mul(const void* gu, void* out, int dtype, int M, int I, int tiled, cudaStream_t stream) {
+// kind: GLU_SILU, GLU_GELU or GLU_CLAMPED (with its limit).
+extern "C" int fd_glu_mul(const void* gu, void* out, int dtype, int M, int I, int tiled, int kind, float limit,
+                          cudaStream_t stream) {
     const size_t total = (size_t)M * I;
     if (total == 0) return 0;
-    FD_REQUIRE(!tiled || I % 8 == 0, -2, "silu_mul: the tiled layout needs a multiple of 8 outputs, got %d", I);
+    FD_REQUIRE(kind >= 0 && kind <= 2, -2, "glu_mul: unknown activation %d", kind);
+    FD_REQUIRE(!tiled || I % 8 == 0, -2, "glu_mul: the tiled layout needs a multiple of 8 outputs, got %d", I);
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == 0) {
-        if (tiled) silu_mul_tiled_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
-        else silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+        if (tiled) silu_mul_tiled_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total, kind, limit);
+        else silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total, kind, limit);
     } else {
-        if (tiled) silu_mul_tiled_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
-        else silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+        if (tiled) silu_mul_tiled_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total, kind, limit);
+        else silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total, kind, limit);
     }
-    return check_launch("silu_mul");
+    return check_launch("glu_mul");
+}
+
+extern "C" int fd_silu_mul(const void* gu, void* out, int dtype, int M, int I, int tiled, cudaStream_t stream) {
+    return fd_glu_mul(gu, out, dtype, M, I, tiled, GLU_SILU, 0.f, stream);
+}
+
+// x <- cap * tanh(x / cap), in place, float.
+extern "C" int fd_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n == 0) return 0;
+    FD_REQUIRE(cap > 0.f, -2, "softcap: the cap must be positive");
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    return launch("softcap", softcap_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(threads), 0, stream,
+                  dim3(1, 1, 1), x, (size_t)n, cap);
 }
 
 // qkv_dtype: element type of `qkv` (0 float, 1 bfloat16); with n_parts > 1 it

@@ -36,15 +36,16 @@ constexpr int MOE_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ logits,
-                 const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ wts, int H, int n_out,
-                 int top) {
+                 const float* __restrict__ correction, const float* __restrict__ bias, int* __restrict__ ids,
+                 float* __restrict__ wts, int H, int n_out, int top) {
     extern __shared__ __align__(16) float z_s[];         // [n_out] logits, then scores; [n_out] choice scores; [H] the row
     float* c_s = z_s + n_out;
     float* x_s = c_s + n_out;
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (logits != nullptr) {
-        for (int o = threadIdx.x; o < n_out; o += blockDim.x) z_s[o] = logits[(size_t)t * n_out + o];
+        for (int o = threadIdx.x; o < n_out; o += blockDim.x)
+            z_s[o] = logits[(size_t)t * n_out + o] + (bias != nullptr ? bias[o] : 0.f);
     } else {
         const T* xr = x + (size_t)t * H;
         for (int k = threadIdx.x; k < H; k += blockDim.x) x_s[k] = to_float(xr[k]);
@@ -66,7 +67,7 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* 
                 for (int k = lane; k < H; k += 32) acc = fmaf(to_float(wr[k]), x_s[k], acc);
             }
             acc = warp_sum(acc);
-            if (lane == 0) z_s[o] = acc;
+            if (lane == 0) z_s[o] = acc + (bias != nullptr ? bias[o] : 0.f);
         }
     }
     __syncthreads();
@@ -159,6 +160,7 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int*
 
 // MODE 0: a[row] = x[sorted_pair[row] / top], out = relu(acc)^2 as T into act [cap, N]
 // MODE 1: a[row] = act[row],                  out = acc as T into y [cap, N]
+// MODE 2: a[row] = x[sorted_pair[row] / top], out = acc as T into [cap, N] (an activation kernel follows)
 template <typename T, int MODE>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restrict__ out,
@@ -174,7 +176,7 @@ moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restri
     const int tid = threadIdx.x;
     if (tid < MOE_MT) {
         const int pr = sorted_pair[tile * MOE_MT + tid];
-        row_s[tid] = pr < 0 ? -1 : (MODE == 0 ? pr / top : tile * MOE_MT + tid);
+        row_s[tid] = pr < 0 ? -1 : (MODE != 1 ? pr / top : tile * MOE_MT + tid);
     }
     __syncthreads();
     const T* we = w + (size_t)e * N * K;
@@ -244,7 +246,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
     const int n0 = blockIdx.x * BN;
     for (int i = tid; i < BM; i += THREADS) {
         const int pr = sorted_pair[tile * BM + i];
-        row_s[i] = pr < 0 ? -1 : (MODE == 0 ? pr / top : tile * BM + i);
+        row_s[i] = pr < 0 ? -1 : (MODE != 1 ? pr / top : tile * BM + i);
     }
     __syncthreads();
     const __nv_bfloat16* we = w + (size_t)tile_expert[tile] * N * K;
@@ -437,8 +439,10 @@ extern "C" int fd_moe_tile_rows(int dtype, int rows_per_expert) { return dtype =
 // x [T, H] and w [n_out, H] of type dtype (0 float32, 1 bfloat16), or logits [T, n_out] float made from them by a
 // matrix product (then x and w are not read); correction [n_out] float or null; ids [T, top] int32 and wts [T, top]
 // float come back.
+// bias [n_out] float or null: added to the logits before the softmax (correction only shifts the choice).
 extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float* logits, const float* correction,
-                            int* ids, float* wts, int T, int H, int n_out, int top, cudaStream_t stream) {
+                            const float* bias, int* ids, float* wts, int T, int H, int n_out, int top,
+                            cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(n_out >= 1 && top >= 1 && top <= n_out && n_out <= 4096, -2,
                "moe_route: %d choices of %d router outputs (at most 4096)", top, n_out);
@@ -448,9 +452,9 @@ extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float
     const int threads = logits != nullptr ? 32 : (n_out >= 32 ? ROUTE_THREADS : ((n_out + 7) / 8 * 8) * 32);
     if (dtype == 0)
         return launch("moe_route", moe_route_kernel<float>, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1),
-                      (const float*)x, (const float*)w, logits, correction, ids, wts, H, n_out, top);
+                      (const float*)x, (const float*)w, logits, correction, bias, ids, wts, H, n_out, top);
     return launch("moe_route", moe_route_kernel<bf16>, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1),
-                  (const bf16*)x, (const bf16*)w, logits, correction, ids, wts, H, n_out, top);
+                  (const bf16*)x, (const bf16*)w, logits, correction, bias, ids, wts, H, n_out, top);
 }
 
 // cap: rows of the grouped buffers, at least P rounded up to whole tiles plus one tile per expert.
@@ -466,21 +470,24 @@ extern "C" int fd_moe_align(const int* ids, int P, int E, int* pair_pos, int* so
                   ids, P, E, pair_pos, sorted_pair, tile_expert, n_tiles, cap, mt);
 }
 
-// mode 0: a = x [T, K], out = act [cap, N] (dtype) = relu(x W_e^T)^2;  mode 1: a = act [cap, K], out = y [cap, N] (dtype).
+// mode 0: a = x [T, K], out = act [cap, N] (dtype) = relu(x W_e^T)^2;  mode 1: a = act [cap, K], out = y [cap, N] (dtype);
+// mode 2: a = x [T, K], out [cap, N] (dtype) = x W_e^T.
 // w [E, N, K].
 // mt: the tile rows the grouping was made with.
 extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, int mode, const int* sorted_pair,
                            const int* tile_expert, const int* n_tiles, int cap, int mt, int top, int N, int K,
                            cudaStream_t stream) {
     if (cap == 0) return 0;
-    FD_REQUIRE(cap % mt == 0 && N > 0 && K > 0, -2, "moe_gemm: bad sizes");
+    FD_REQUIRE(cap % mt == 0 && N > 0 && K > 0 && mode >= 0 && mode <= 2, -2, "moe_gemm: bad sizes or mode");
     if (dtype == 1 && K % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0) {
         if (mt == 128) {
             if (mode == 0) return launch_moe_mma<128, 128, 2, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+            if (mode == 2) return launch_moe_mma<128, 128, 2, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
             return launch_moe_mma<128, 128, 2, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
         }
         if (mt == 32) {
             if (mode == 0) return launch_moe_mma<32, 64, 1, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+            if (mode == 2) return launch_moe_mma<32, 64, 1, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
             return launch_moe_mma<32, 64, 1, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
         }
     }
@@ -490,8 +497,9 @@ extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, i
 #define FD_MG(T_, M_)                                                                                                \
     return launch("moe_gemm", moe_gemm_kernel<T_, M_>, grid, dim3(MOE_THREADS), 0, stream, dim3(1, 1, 1), (const T_*)a, \
                   (const T_*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K)
-    if (dtype == 0) { if (mode == 0) FD_MG(float, 0); FD_MG(float, 1); }
+    if (dtype == 0) { if (mode == 0) FD_MG(float, 0); if (mode == 2) FD_MG(float, 2); FD_MG(float, 1); }
     if (mode == 0) FD_MG(bf16, 0);
+    if (mode == 2) FD_MG(bf16, 2);
     FD_MG(bf16, 1);
 #undef FD_MG
 }

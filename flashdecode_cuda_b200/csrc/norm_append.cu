@@ -1,0 +1,88 @@
+// What stands between an attention mixer's packed projection and its attention
+// kernel when nothing is rotated: q and k are each normed over their WHOLE
+// projection (all heads at once, before they are split into heads), q goes to
+// its buffer, k and v to the paged cache at the token's position.
+//
+//   proj  [T, ld]: columns [0, nq) are q, [nq, nq + nk) are k, [nq + nk, nq + nk + nv) are v
+//   q_out [T, nq]                      q / sqrt(mean(q^2) + eps) * q_w   (q_w null: q as it is)
+//   k_pool [blocks, n_kv, block_size, nk / n_kv]   the same with k_w
+//   v_pool [blocks, n_kv, block_size, nv / n_kv]   nv == 0: no values are kept (the keys serve as values)
+//
+// With n_kv = 1 and nv = 0 the "key" is any normed vector per position, e.g. the
+// low-rank latent that a latent-attention mixer makes its keys and values from.
+// Sums of squares and the norm are float; a CTA per token.
+#include "common.cuh"
+
+namespace fd {
+
+template <typename T>
+__global__ void norm_append_kernel(const T* __restrict__ proj, int ld, T* __restrict__ q_out,
+                                   const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                   const int* __restrict__ tok_row, const int* __restrict__ tok_pos,
+                                   const int* __restrict__ row_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                   const int* __restrict__ block_table, int max_blocks, int num_blocks, int block_size,
+                                   int nq, int nk, int nv, int n_kv, int write_kv, int* status) {
+    __shared__ float red[40];
+    const int t = blockIdx.x;
+    const int slot = row_slot[tok_row[t]];
+    if (slot < 0) return;             // padding row of a fixed-size batch
+    const T* row = proj + (size_t)t * ld;
+    float sq = 0.f, sk = 0.f;
+    if (q_w != nullptr)
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = to_float(row[i]); sq += v * v; }
+    if (k_w != nullptr)
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = to_float(row[nq + i]); sk += v * v; }
+    const float rq = q_w != nullptr ? rsqrtf(block_sum(sq, red) / (float)nq + eps) : 1.f;
+    const float rk = k_w != nullptr ? rsqrtf(block_sum(sk, red) / (float)nk + eps) : 1.f;
+    T* qo = q_out + (size_t)t * nq;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const float v = to_float(row[i]);
+        qo[i] = q_w != nullptr ? from_float<T>(v * rq * q_w[i]) : row[i];
+    }
+    if (!write_kv) return;
+    const int pos = tok_pos[t];
+    const int blk = pos >= 0 && pos / block_size < max_blocks ? block_table[(size_t)slot * max_blocks + pos / block_size] : -1;
+    if (blk < 0 || blk >= num_blocks) {
+        if (threadIdx.x == 0) set_status(status, STATUS_BAD_BLOCK);
+        return;
+    }
+    const int d = nk / n_kv;
+    T* kd = k_pool + ((size_t)blk * n_kv * block_size + (pos % block_size)) * d;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int h = i / d, j = i - h * d;
+        const float v = to_float(row[nq + i]);
+        kd[(size_t)h * block_size * d + j] = k_w != nullptr ? from_float<T>(v * rk * k_w[i]) : row[nq + i];
+    }
+    if (nv > 0) {
+        const int dv = nv / n_kv;
+        T* vd = v_pool + ((size_t)blk * n_kv * block_size + (pos % block_size)) * dv;
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            const int h = i / dv, j = i - h * dv;
+            vd[(size_t)h * block_size * dv + j] = row[nq + nk + i];
+        }
+    }
+}
+
+}  // namespace fd
+
+using namespace fd;
+typedef __nv_bfloat16 bf16;
+
+// dtype (0 float32, 1 bfloat16): proj, q_out and the pools alike.  q_w [nq], k_w [nk]: float or null.
+extern "C" int fd_norm_append(const void* proj, int ld, void* q_out, int dtype, const float* q_w, const float* k_w,
+                              float eps, const int* tok_row, const int* tok_pos, const int* row_slot, void* k_pool,
+                              void* v_pool, const int* block_table, int max_blocks, int num_blocks, int block_size, int T,
+                              int nq, int nk, int nv, int n_kv, int write_kv, int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    FD_REQUIRE(nq > 0 && nk > 0 && nv >= 0 && n_kv > 0 && nk % n_kv == 0 && nv % n_kv == 0 && ld >= nq + nk + nv, -2,
+               "norm_append: %d + %d + %d columns of %d for %d key heads", nq, nk, nv, ld, n_kv);
+    FD_REQUIRE(block_size > 0 && (nv == 0 || v_pool != nullptr), -2, "norm_append: bad cache arguments");
+    const int threads = nq + nk >= 1024 ? 256 : 128;
+    if (dtype == 0)
+        return launch("norm_append", norm_append_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
+                      (const float*)proj, ld, (float*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (float*)k_pool,
+                      (float*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv, status);
+    return launch("norm_append", norm_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)proj, ld, (bf16*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (bf16*)k_pool,
+                  (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv, status);
+}

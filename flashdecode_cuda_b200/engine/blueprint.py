@@ -88,8 +88,13 @@ class ModelBlueprint:
     max_positions: int                        # longest sequence the configuration allows
     # operations on the whole residual stream between layers, by the name schedule entries ask for
     stream_ops: Dict[str, PartSpec] = field(default_factory=dict)
+    # lanes of the residual stream: the step's stream is [T, lanes * hidden_size] float32, every lane equal to the
+    # embedding output at the start; the blocks and the final norm of such a model are the ones that know lanes
+    lanes: int = 1
 
     def validate(self) -> None:
+        if self.lanes < 1 or (self.lanes > 1 and self.stream_ops):
+            raise ValueError("lanes must be positive, and stream operations are defined on a stream of one lane")
         for i, run in enumerate(self.schedule):
             if run.before is not None and run.before not in self.stream_ops:
                 raise ValueError(f"schedule entry {i} names the stream operation {run.before!r}, "

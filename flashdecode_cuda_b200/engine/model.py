@@ -383,12 +383,19 @@ class Model:
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """Run the parts over a prepared step.  Returns logits [n_want, V]
         (float32, a view of workspace memory that the next step overwrites)."""
-        resid = ctx.ws.get("resid", (ctx.T, self.hidden_size), torch.float32)
-        self.embedding.forward(ctx, resid)
-        if self.trace is not None:
-            self.trace["embed"] = resid.detach().float().cpu().clone()
+        lanes = self.blueprint.lanes
+        resid = ctx.ws.get("resid", (ctx.T, lanes * self.hidden_size), torch.float32)
         embedded = None
-        if self.stream_ops:
+        if lanes > 1:
+            # a stream of several lanes: every lane starts as the embedding output
+            embedded = ctx.ws.get("embedded", (ctx.T, self.hidden_size), torch.float32)
+            self.embedding.forward(ctx, embedded)
+            K.lanes_fill(embedded, resid, lanes)
+        else:
+            self.embedding.forward(ctx, resid)
+        if self.trace is not None:
+            self.trace["embed"] = (resid if embedded is None else embedded).detach().float().cpu().clone()
+        if self.stream_ops and embedded is None:
             # stream operations may read the embedding output again later in the step
             embedded = ctx.ws.get("embedded", (ctx.T, self.hidden_size), torch.float32)
             embedded.copy_(resid)
@@ -407,8 +414,7 @@ class Model:
             ctx.upcoming = (op_next if op_next is not None else (self.head if last else nxt)).first_weights()
             delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[i])
             if self.trace is not None:
-                d = 0 if delta is None else (delta.float().sum(0) if delta.dim() == 3 else delta.float())
-                self.trace[f"layer.{i}"] = (resid + d).cpu()
+                self.trace[f"layer.{i}"] = self.blocks[run.layer].stream_state(resid, delta).cpu()
         if ctx.n_want == 0:
             return None
         xn = ctx.ws.get("final_normed", (ctx.n_want, self.hidden_size), self.dtype)

@@ -101,7 +101,14 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_add_concat": [P, I, P, P, P, I, I, I, P],
         "fd_relu2": [P, P, I, LL, P],
         "fd_moe_tile_rows": [I, I],
-        "fd_moe_route": [P, P, I, P, P, P, P, I, I, I, I, P],
+        "fd_moe_route": [P, P, I, P, P, P, P, P, I, I, I, I, P],
+        "fd_glu_mul": [P, P, I, I, I, I, I, F, P],
+        "fd_softcap": [P, LL, F, P],
+        "fd_lanes_norm": [P, I, I, LL, P, P, P, P, I, P, P, F, P, I, P, I, I, I, P],
+        "fd_lanes_fill": [P, P, I, I, I, P],
+        "fd_lanes_sum": [P, I, P, P, P, P, P, I, I, I, P],
+        "fd_norm_append": [P, I, P, I, P, P, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+        "fd_head_gemm": [P, P, P, I, I, I, I, I, P],
         "fd_moe_align": [P, I, I, P, P, P, P, I, I, P],
         "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, P],
         "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
@@ -236,6 +243,96 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, tiled: bool = False) -> N
     M, I2 = gate_up.shape
     assert out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
     _check(lib().fd_silu_mul(_ptr(gate_up), _ptr(out), _dt(out.dtype), M, I2 // 2, int(tiled), _stream()))
+
+
+GLU_SILU, GLU_GELU_TANH, GLU_CLAMPED = 0, 1, 2
+GLU_KINDS = {"silu": GLU_SILU, "gelu_tanh": GLU_GELU_TANH, "clamped_swish": GLU_CLAMPED}
+
+
+def glu_mul(gate_up: torch.Tensor, out: torch.Tensor, kind: int, limit: float = 0.0, tiled: bool = False) -> None:
+    """out[m, i] = act(gate_i, up_i) with ``gate_up`` [M, 2I] = [gate | up] (or tiles of 8 + 8 columns).  ``kind``:
+    GLU_SILU g sigmoid(g) u; GLU_GELU_TANH the tanh form of GELU of g, times u; GLU_CLAMPED g' sigmoid(1.702 g') (u' + 1)
+    with g' = min(g, limit) and u' = clamp(u, -limit, limit).  Float arithmetic, one rounding."""
+    M, I2 = gate_up.shape
+    assert out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
+    _check(lib().fd_glu_mul(_ptr(gate_up), _ptr(out), _dt(out.dtype), M, I2 // 2, int(tiled), int(kind), float(limit),
+                            _stream()))
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place; x float32."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib().fd_softcap(_ptr(x), x.numel(), float(cap), _stream()))
+
+
+def lanes_norm(y: Optional[torch.Tensor], gain: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+               back: Optional[torch.Tensor], lanes: torch.Tensor, read: Optional[torch.Tensor], weight: torch.Tensor,
+               eps: float, out: torch.Tensor, n_lanes: int, rows: Optional[torch.Tensor] = None,
+               n_out: Optional[int] = None, write_lanes: bool = True) -> None:
+    """The step between two sub-layers on a residual stream of ``n_lanes`` lanes, ``lanes`` [T, n_lanes * H] float32:
+    first the pending update X'[t] = sum_s mix[s, t] X[s] + back[t] * gain * y (``y`` [T, H], or float partial sums
+    [parts, T, H]; None: nothing pending), written back when ``write_lanes``; then out[j] = rmsnorm(sum_s read[s]
+    X'[s]) * weight for row j (or rows[j]).  gain [H], mix [S, S], back [S], read [S]: float32 or None (ones, the unit
+    matrix)."""
+    H = weight.numel()
+    assert lanes.dtype == torch.float32 and lanes.shape[-1] == n_lanes * H and out.shape[-1] == H
+    for t in (gain, mix, back, read, weight):
+        assert t is None or t.dtype == torch.float32
+    n_parts, part_stride = 1, 0
+    if y is not None and y.dim() == 3:
+        n_parts, part_stride = y.shape[0], y.shape[1] * y.shape[2]
+    if n_out is None:
+        n_out = rows.numel() if rows is not None else lanes.shape[0]
+    _check(lib().fd_lanes_norm(_ptr(y), _dt(y.dtype) if y is not None else _dt(out.dtype), n_parts, part_stride,
+                               _ptr(gain), _ptr(mix), _ptr(back), _ptr(lanes), int(write_lanes), _ptr(read), _ptr(weight),
+                               float(eps), _ptr(out), _dt(out.dtype), _ptr(rows), n_out, H, n_lanes, _stream()))
+
+
+def lanes_fill(src: torch.Tensor, lanes: torch.Tensor, n_lanes: int) -> None:
+    """Every lane of ``lanes`` [T, n_lanes * H] <- ``src`` [T, H]; float32."""
+    T, H = src.shape
+    assert src.dtype == lanes.dtype == torch.float32 and lanes.shape == (T, n_lanes * H)
+    _check(lib().fd_lanes_fill(_ptr(src), _ptr(lanes), T, H, n_lanes, _stream()))
+
+
+def lanes_sum(y: Optional[torch.Tensor], gain: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+              back: Optional[torch.Tensor], lanes: torch.Tensor, out: torch.Tensor, n_lanes: int) -> None:
+    """out [T, H] float32 = the lanes added up, after the pending update (as in ``lanes_norm``) if ``y`` is given."""
+    T, H = out.shape
+    assert lanes.dtype == out.dtype == torch.float32 and lanes.shape == (T, n_lanes * H)
+    assert y is None or y.shape == (T, H)
+    _check(lib().fd_lanes_sum(_ptr(y), _dt(y.dtype) if y is not None else 0, _ptr(gain), _ptr(mix), _ptr(back),
+                              _ptr(lanes), _ptr(out), T, H, n_lanes, _stream()))
+
+
+def norm_append(proj: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
+                k_weight: Optional[torch.Tensor], eps: float, tok_row: torch.Tensor, tok_pos: torch.Tensor,
+                row_slot: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor], block_table: torch.Tensor,
+                n_kv: int, write_kv: bool, status: torch.Tensor) -> None:
+    """``proj`` [T, >= nq + nk + nv] = [q | k | v]: q (normed over all its nq columns with ``q_weight``, or as it is) to
+    ``q_out`` [T, nq]; k (normed over all its nk columns with ``k_weight``, or as it is) and v to the pools at each
+    token's position.  ``v_pool`` None: nothing but the keys is kept.  Norm weights float32."""
+    T, ld = proj.shape
+    nq = q_out.shape[1]
+    num_blocks, kvh, block_size, d = k_pool.shape
+    nk = n_kv * d
+    nv = 0 if v_pool is None else n_kv * v_pool.shape[-1]
+    assert kvh == n_kv and proj.dtype == q_out.dtype == k_pool.dtype and proj.is_contiguous()
+    assert q_weight is None or (q_weight.dtype == torch.float32 and q_weight.numel() == nq)
+    assert k_weight is None or (k_weight.dtype == torch.float32 and k_weight.numel() == nk)
+    _check(lib().fd_norm_append(_ptr(proj), ld, _ptr(q_out), _dt(proj.dtype), _ptr(q_weight), _ptr(k_weight), float(eps),
+                                _ptr(tok_row), _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool),
+                                _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, nq, nk, nv, n_kv,
+                                int(write_kv), _ptr(status), _stream()))
+
+
+def head_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h, :] = w[h] a[t, h, :]: a [T, heads * K], w [heads, N, K], out [T, heads * N]; float accumulation."""
+    heads, N, Kd = w.shape
+    T = a.shape[0]
+    assert a.shape == (T, heads * Kd) and out.shape == (T, heads * N) and a.dtype == w.dtype == out.dtype
+    assert a.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    _check(lib().fd_head_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), T, heads, N, Kd, _stream()))
 
 
 def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
@@ -640,19 +737,22 @@ ROUTE_FUSED_MAX_ROW = 8192      # widest row of x the routing kernel takes into 
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
-              wts: torch.Tensor, logits: Optional[torch.Tensor] = None) -> None:
+              wts: torch.Tensor, logits: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
     """Per row of x [T, H]: softmax scores over the rows of ``router`` [n_out, H] (float arithmetic), the ``top``
     outputs with the largest score + correction into ``ids`` [T, top] (int32), and their scores over their sum
     (+ 1e-20) into ``wts`` [T, top] (float32).  ``logits`` [T, n_out] float32: the router's outputs made by a matrix
-    product beforehand (steps of many tokens); without them the kernel makes them itself, a token per CTA."""
+    product beforehand (steps of many tokens); without them the kernel makes them itself, a token per CTA.
+    ``bias`` [n_out] float32 is added to the logits before the softmax.  The chosen scores over their sum are the
+    softmax over the chosen logits alone."""
     T, H = x.shape
     n_out, top = router.shape[0], ids.shape[1]
     assert router.shape == (n_out, H) and router.dtype == x.dtype and ids.dtype == torch.int32
     assert wts.dtype == torch.float32 and wts.shape == ids.shape == (T, top)
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n_out)
     assert logits is None or (logits.dtype == torch.float32 and logits.shape == (T, n_out))
-    _check(lib().fd_moe_route(_ptr(x), _ptr(router), _dt(x.dtype), _ptr(logits), _ptr(correction), _ptr(ids), _ptr(wts),
-                              T, H, n_out, top, _stream()))
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out)
+    _check(lib().fd_moe_route(_ptr(x), _ptr(router), _dt(x.dtype), _ptr(logits), _ptr(correction), _ptr(bias), _ptr(ids),
+                              _ptr(wts), T, H, n_out, top, _stream()))
 
 
 def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_pair: torch.Tensor,
@@ -668,16 +768,17 @@ def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, sorted_pair: torch.Tensor,
-             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int) -> None:
+             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int, plain: bool = False) -> None:
     """Grouped product with the experts' stacked matrices w [E, N, K].  ``down`` False: a = x [T, K] (rows gathered
     through the grouping), out [cap, N] = relu(x w_e^T)^2 in a's dtype; True: a = the grouped activations [cap, K],
-    out [cap, N] in a's dtype.  ``mt``: the tile rows the grouping was made with.  bfloat16 with K a multiple of 8 runs on
+    out [cap, N] in a's dtype.  ``plain`` (with ``down`` False): no activation, out = x w_e^T (a gated activation follows
+    in a kernel of its own).  ``mt``: the tile rows the grouping was made with.  bfloat16 with K a multiple of 8 runs on
     the tensor cores, everything else on the CUDA cores (tiles of 32 rows only)."""
     E, N, Kd = w.shape
     cap = sorted_pair.numel()
     assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N)
     assert out.dtype == a.dtype and (not down or a.shape[0] == cap)
-    _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), int(down), _ptr(sorted_pair), _ptr(tile_expert),
+    _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), 1 if down else (2 if plain else 0), _ptr(sorted_pair), _ptr(tile_expert),
                              _ptr(n_tiles), cap, mt, top, N, Kd, _stream()))
 
 

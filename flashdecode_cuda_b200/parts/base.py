@@ -57,16 +57,18 @@ class Runtime:
 class KVRequest:
     """Paged key/value storage a mixer needs for each sequence.  ``window``: only the last
     so many keys are ever read; ``chunk``: only the keys of the query's own chunk of so many
-    positions; ``v_head_dim``: size of a value head where it differs from ``head_dim``."""
+    positions; ``v_head_dim``: size of a value head where it differs from ``head_dim``; ``keys_only``: one
+    vector per position and head is kept and read both as key and as value."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     v_head_dim: Optional[int] = None
+    keys_only: bool = False
 
     def key(self):
         v = None if self.v_head_dim in (None, self.head_dim) else self.v_head_dim
-        return (self.n_kv_heads, self.head_dim, self.window, self.chunk, v)
+        return (self.n_kv_heads, self.head_dim, self.window, self.chunk, v, self.keys_only)
 
 
 @dataclass
@@ -148,6 +150,14 @@ class Block(Part):
     kind = "block"
     # True: ``forward`` takes the incoming ``delta`` as float32 partial sums [parts, T, H] too
     accepts_parts = False
+
+    def stream_state(self, resid: torch.Tensor, delta) -> torch.Tensor:
+        """The residual stream [T, H] (float32, a new tensor) as it stands once ``delta``, what this block's ``forward``
+        returned, has been added: what a per-layer trace records.  A block whose stream or delta has another form
+        says here how they combine."""
+        if delta is None:
+            return resid.clone()
+        return resid + (delta.float().sum(0) if delta.dim() == 3 else delta.float())
 
 
 class Head(Part):

@@ -73,3 +73,58 @@ class SwiGLU(FeedForward):
             parts = ws.get("ffn_out_parts", (MAX_PARTS, T, self.hidden_size), torch.float32)
         return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts, status=self.rt.status,
                       upcoming=ctx.upcoming)
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(FeedForward):
+    """down( act(gate(x)) * up(x) ) with a choice of activation and biases on all three projections.
+
+    ``activation``: ``"silu"`` or ``"gelu_tanh"`` (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))).  ``bias``: every
+    projection has one.  Tensors ``<prefix>.gate`` / ``.up`` / ``.down`` (stored [out, in]) and, with biases,
+    ``.gate.b`` / ``.up.b`` / ``.down.b``.  gate and up are one packed product; the activation is computed in float32
+    from the product's output and rounded once.
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh",
+                 bias: bool = True):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"{prefix}: unknown activation {activation!r}; known: silu, gelu_tanh")
+        self.prefix, self.hidden_size, self.inter = prefix, hidden_size, intermediate_size
+        self.activation, self.bias = activation, bool(bias)
+        self.kind = K.GLU_KINDS[activation]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H, I = self.prefix, self.hidden_size, self.inter
+        specs = [TensorSpec(f"{p}.gate", (I, H), init="unit"), TensorSpec(f"{p}.up", (I, H), init="unit"),
+                 TensorSpec(f"{p}.down", (H, I), init="unit")]
+        if self.bias:
+            specs += [TensorSpec(f"{p}.gate.b", (I,), "vector", init="bias"),
+                      TensorSpec(f"{p}.up.b", (I,), "vector", init="bias"),
+                      TensorSpec(f"{p}.down.b", (H,), "vector", init="bias")]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors.pop(f"{p}.gate"), tensors.pop(f"{p}.up")], dim=0).contiguous()
+        self.w_down = tensors[f"{p}.down"]
+        self.b_gate_up = self.b_down = None
+        if self.bias:
+            self.b_gate_up = torch.cat([tensors.pop(f"{p}.gate.b"), tensors.pop(f"{p}.up.b")]).contiguous()
+            self.b_down = tensors[f"{p}.down.b"]
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_gate_up
+
+    def forward(self, ctx, x: torch.Tensor, parts_ok: bool = False) -> torch.Tensor:
+        T, ws = ctx.T, ctx.ws
+        gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
+        matmul(x, self.w_gate_up, self.b_gate_up, gu, status=self.rt.status)
+        act = ws.get("ffn_act", (T, self.inter), x.dtype)
+        K.glu_mul(gu, act, self.kind)
+        out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
+        return matmul(act, self.w_down, self.b_down, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status,
+                      upcoming=ctx.upcoming)

@@ -30,7 +30,10 @@ class RoutedExperts(FeedForward):
         w      = s[chosen] / (sum of s[chosen] + 1e-20)
         out    = sum over chosen e of w_e * expert_e(h)  +  shared(h)
 
-    An expert, and the shared expert, is down(act(up h)) with act = relu^2 and no biases.  The last
+    An expert, and the shared expert, is down(act(up h)) with act = relu^2 and no biases; with ``expert_act =
+    "clamped_swish"`` an expert is gated instead: g = min(gate h, limit), u = clamp(up h, -limit, limit),
+    down(g sigmoid(1.702 g) (u + 1)) (tensors ``.e<i>.gate`` too).  ``router_bias``: ``<prefix>.router.b`` is added to
+    the router's outputs before the softmax; w is then the softmax over the chosen outputs alone.  The last
     ``n_identity`` router outputs are identity experts: they have no tensors and pass h on.  ``shared_ff``
     None: no shared expert.
 
@@ -41,20 +44,28 @@ class RoutedExperts(FeedForward):
     """
 
     def __init__(self, prefix: str, hidden_size: int, n_experts: int, top: int, expert_ff: int, n_identity: int = 0,
-                 shared_ff: Optional[int] = None, correction: bool = True):
+                 shared_ff: Optional[int] = None, correction: bool = True, expert_act: str = "relu2",
+                 limit: Optional[float] = None, router_bias: bool = False):
         if n_experts < 0 or n_identity < 0 or not (1 <= top <= n_experts + n_identity) or expert_ff < 1:
             raise ValueError(f"{prefix}: {top} choices among {n_experts} experts and {n_identity} identity experts")
         self.prefix, self.hidden_size = prefix, hidden_size
         self.E, self.n_identity, self.top, self.ff, self.shared_ff = n_experts, n_identity, top, expert_ff, shared_ff
         self.has_correction = correction
+        if expert_act not in ("relu2", "clamped_swish") or (expert_act == "clamped_swish" and not (limit and limit > 0)):
+            raise ValueError(f"{prefix}: expert activation {expert_act!r} (relu2, or clamped_swish with a positive limit)")
+        self.gated, self.limit, self.router_bias = expert_act == "clamped_swish", limit, bool(router_bias)
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, H = self.prefix, self.hidden_size
         specs = []
         for e in range(self.E):
+            if self.gated:
+                specs.append(TensorSpec(f"{p}.e{e}.gate", (self.ff, H), init="unit"))
             specs += [TensorSpec(f"{p}.e{e}.up", (self.ff, H), init="unit"),
                       TensorSpec(f"{p}.e{e}.down", (H, self.ff), init="unit")]
         specs.append(TensorSpec(f"{p}.router", (self.E + self.n_identity, H), init="unit"))
+        if self.router_bias:
+            specs.append(TensorSpec(f"{p}.router.b", (self.E + self.n_identity,), "vector", init="bias"))
         if self.has_correction:
             specs.append(TensorSpec(f"{p}.correction", (self.E + self.n_identity,), "vector", init="bias"))
         if self.shared_ff is not None:
@@ -66,12 +77,17 @@ class RoutedExperts(FeedForward):
         self.rt = rt
         p = self.prefix
         if self.E:
-            self.w_up = torch.stack([tensors.pop(f"{p}.e{e}.up") for e in range(self.E)]).contiguous()       # [E, ff, H]
+            if self.gated:       # [E, 2 ff, H]: an expert's gate rows, then its up rows: one product
+                self.w_up = torch.stack([torch.cat([tensors.pop(f"{p}.e{e}.gate"), tensors.pop(f"{p}.e{e}.up")])
+                                         for e in range(self.E)]).contiguous()
+            else:
+                self.w_up = torch.stack([tensors.pop(f"{p}.e{e}.up") for e in range(self.E)]).contiguous()   # [E, ff, H]
             self.w_down = torch.stack([tensors.pop(f"{p}.e{e}.down") for e in range(self.E)]).contiguous()   # [E, H, ff]
         else:
             self.w_up = self.w_down = None
         self.router = tensors[f"{p}.router"]
         self.correction = tensors[f"{p}.correction"].float().contiguous() if self.has_correction else None
+        self.r_bias = tensors[f"{p}.router.b"].float().contiguous() if self.router_bias else None
         self.s_up = tensors.get(f"{p}.shared.up")
         self.s_down = tensors.get(f"{p}.shared.down")
 
@@ -112,7 +128,7 @@ class RoutedExperts(FeedForward):
             # token's scores do not change by a bit with its neighbours
             logits = ws.get("moe_logits", (T, self.router.shape[0]), torch.float32)
             matmul(x, self.router, None, logits, status=self.rt.status)
-        K.moe_route(x, self.router, self.correction, ids, wts, logits)
+        K.moe_route(x, self.router, self.correction, ids, wts, logits, bias=self.r_bias)
         # (the routed experts follow on the main stream; the shared expert's stream joins before the combine)
         y = pair_pos = None
         pair_pos = ws.get("moe_pair_pos", (T * top,), torch.int32)
@@ -125,15 +141,25 @@ class RoutedExperts(FeedForward):
             K.moe_align(ids, self.E, pair_pos, sorted_pair, tile_expert, n_tiles, mt)
             act = ws.get("moe_act", (cap, self.ff), x.dtype)
             y = ws.get("moe_y", (cap, H), x.dtype)
-            if (mt == 128 and GROUPED_GEMM == "auto" and K.gemm_tc_grouped_supported(self.ff, H)
+            n_up = self.w_up.shape[1]                   # ff, or 2 ff for gated experts
+            gu = ws.get("moe_gu", (cap, n_up), x.dtype) if self.gated else None
+            if (mt == 128 and GROUPED_GEMM == "auto" and K.gemm_tc_grouped_supported(n_up, H)
                     and K.gemm_tc_grouped_supported(H, self.ff)):
                 # prompts: the grouped rows as one matrix, then both products on the tcgen05 tensor cores
                 xs = ws.get("moe_xs", (cap, H), x.dtype)
                 K.moe_gather(x, xs, sorted_pair, n_tiles, top, mt)
-                K.gemm_tc_grouped(xs, self.w_up, act, True, tile_expert, n_tiles, self.rt.status)
+                if self.gated:
+                    K.gemm_tc_grouped(xs, self.w_up, gu, False, tile_expert, n_tiles, self.rt.status)
+                    K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit)
+                else:
+                    K.gemm_tc_grouped(xs, self.w_up, act, True, tile_expert, n_tiles, self.rt.status)
                 K.gemm_tc_grouped(act, self.w_down, y, False, tile_expert, n_tiles, self.rt.status)
             else:
-                K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
+                if self.gated:
+                    K.moe_gemm(x, self.w_up, gu, False, sorted_pair, tile_expert, n_tiles, top, mt, plain=True)
+                    K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit)
+                else:
+                    K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
                 K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top, mt)
         out = ws.get("ffn_out", (T, H), x.dtype)
         K.moe_combine(y, x, shared, ids, wts, pair_pos, out, self.E)

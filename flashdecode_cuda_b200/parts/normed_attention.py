@@ -1,0 +1,190 @@
+"""Attention mixers without a rotation: grouped-query attention whose q and k are normed over their whole
+projection, with a sliding window; and latent attention, which keeps one low-rank vector per position and makes
+every head's keys and values from it."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_part
+from ..weights.spec import TensorSpec
+from .attention import FP32_SPLIT_LEN, plan_splits
+from .base import KVRequest, LayerCache, Mixer, Runtime
+from .linear import matmul
+
+
+def decode_splits(ctx, n_q: int, n_kv: int, v_dim: int, dtype: torch.dtype, rt: Runtime):
+    """(n_splits, split_len, scratch) of a step's attention: a step of single tokens cuts every sequence's keys into
+    splits (float32: of a fixed length, so that where a sequence's partial sums are cut depends on its own length only;
+    bfloat16: by the batch's size); any other step does not."""
+    if ctx.max_q_len != 1:
+        return 1, 0, None
+    if dtype == torch.float32:
+        split_len = FP32_SPLIT_LEN
+        n_splits = max(1, -(-ctx.kv_len_bound // split_len))
+    else:
+        n_splits, split_len = plan_splits(ctx.n_rows, n_kv, ctx.kv_len_bound, rt.sm_count)
+    scratch = None
+    if n_splits > 1:
+        scratch = ctx.ws.get("attn_scratch", (K.attention_scratch_floats(ctx.T, n_q, v_dim, n_splits),), torch.float32)
+    return n_splits, split_len, scratch
+
+
+def _head_sizes_ok(prefix: str, **sizes: int) -> None:
+    for what, n in sizes.items():
+        if n < 8 or n > 256 or n % 8 != 0:
+            raise ValueError(f"{prefix}: {what.replace('_', ' ')} {n} is not taken: the attention kernels take multiples "
+                             f"of 8 from 8 to 256")
+
+
+@register_part("mixer", "qk_normed_attention")
+class QKNormedAttention(Mixer):
+    """For the mixer's input h [T, hidden]:
+
+        q, k, v = W_q h, W_k h, W_v h                           (no biases)
+        q       = q / sqrt(mean(q^2) + eps) * w_q               over ALL of q's n_heads * head_dim values at once,
+        k       = k / sqrt(mean(k^2) + eps) * w_k               likewise; then both are split into heads
+        a       = softmax over the visible keys of (q . k) * scale; query head h reads key/value head
+                  h // (n_heads / n_kv_heads); value heads have ``v_head_dim`` dimensions
+        out     = W_o a
+
+    Nothing is rotated: positions enter through visibility alone.  Visible keys of the query at position i: j <= i,
+    and with a ``window`` only i - j < window.  ``qk_norm`` False: q and k are used as projected.  One packed
+    product gives q, k and v.  Tensors ``<prefix>.q`` / ``.k`` / ``.v`` / ``.o`` (stored [out, in]), ``.q.norm``,
+    ``.k.norm``.  The norms are float32 in both dtypes.
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
+                 scale: float, eps: float, window: Optional[int] = None, qk_norm: bool = True):
+        _head_sizes_ok(prefix, head_size=head_dim, value_head_size=v_head_dim)
+        if n_kv_heads < 1 or n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 64:
+            raise ValueError(f"{prefix}: {n_heads} query heads for {n_kv_heads} key/value heads: the kernels take whole "
+                             f"groups of up to 64 query heads per key/value head")
+        if window is not None and window < 1:
+            raise ValueError(f"{prefix}: a window of {window} positions")
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.n_q, self.n_kv, self.d, self.dv = n_heads, n_kv_heads, head_dim, v_head_dim
+        self.scale, self.eps, self.window, self.qk_norm = float(scale), float(eps), window, qk_norm
+
+    def _sizes(self):
+        return (("q", self.n_q * self.d), ("k", self.n_kv * self.d), ("v", self.n_kv * self.dv))
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        specs = [TensorSpec(f"{p}.{n}", (c, H), init="unit") for n, c in self._sizes()]
+        if self.qk_norm:
+            specs += [TensorSpec(f"{p}.q.norm", (self.n_q * self.d,), "vector", init="norm"),
+                      TensorSpec(f"{p}.k.norm", (self.n_kv * self.d,), "vector", init="norm")]
+        specs.append(TensorSpec(f"{p}.o", (H, self.n_q * self.dv), init="unit"))
+        return specs
+
+    def kv_request(self) -> KVRequest:
+        return KVRequest(self.n_kv, self.d, self.window, None, self.dv)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_in = torch.cat([tensors.pop(f"{p}.{n}") for n, _ in self._sizes()], dim=0).contiguous()
+        self.q_norm = tensors[f"{p}.q.norm"].float().contiguous() if self.qk_norm else None
+        self.k_norm = tensors[f"{p}.k.norm"].float().contiguous() if self.qk_norm else None
+        self.w_o = tensors[f"{p}.o"]
+
+    def weight_bytes(self) -> int:
+        return self.w_in.numel() * self.w_in.element_size() + self.w_o.numel() * self.w_o.element_size()
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_in
+
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, ws, rt = ctx.T, ctx.ws, self.rt
+        proj = ws.get("nat_proj", (T, self.w_in.shape[0]), x.dtype)
+        matmul(x, self.w_in, None, proj, status=rt.status)
+        q = ws.get("nat_q", (T, self.n_q * self.d), x.dtype)
+        K.norm_append(proj, q, self.q_norm, self.k_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool,
+                      lc.v_pool, lc.group.table, self.n_kv, lc.writes, rt.status)
+        attn = ws.get("nat_attn", (T, self.n_q * self.dv), x.dtype)
+        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, self.n_kv, self.dv, x.dtype, rt)
+        K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
+                    ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d, self.scale,
+                    self.window or 0, n_splits, split_len, scratch, rt.status)
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        return matmul(attn, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """For the mixer's input h [T, hidden], with ``n_heads`` heads, ``head_dim`` query/key and ``v_head_dim`` value
+    dimensions per head and a latent of ``kv_rank`` dimensions:
+
+        q   = W_q h                                        (no rotated part)
+        c   = (W_dkv h) / sqrt(mean((W_dkv h)^2) + eps) * w_c           the latent: all that is cached
+        k_h = U_h c,  v_h = V_h c                          (U = ``.uk`` [heads * head_dim, kv_rank], V = ``.uv``, head by head)
+        a_h = softmax over the visible keys j of (q_h . k_h[j]) * scale
+        out = W_o [a_1 V-values ... ]
+
+    computed without ever expanding the cached positions: (q_h . U_h c) = (U_h^T q_h) . c, so the queries are taken
+    into the latent's basis (one small product per head), attention runs over the cached latents as ONE key/value head
+    of size ``kv_rank`` that all query heads share and that serves as key and as value, and V_h is applied to each
+    head's attended latent afterwards.  Visible keys: j <= i, and with a ``window`` only i - j < window.
+    Tensors ``<prefix>.q``, ``.dkv``, ``.dkv.norm``, ``.uk``, ``.uv``, ``.o``.
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int, kv_rank: int,
+                 scale: float, eps: float, window: Optional[int] = None):
+        _head_sizes_ok(prefix, latent_size=kv_rank)
+        if n_heads < 1 or n_heads > 64 or head_dim < 1 or v_head_dim < 1:
+            raise ValueError(f"{prefix}: {n_heads} heads of {head_dim} / {v_head_dim}: the attention kernel takes up to 64 "
+                             f"query heads on the one latent")
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.n_q, self.d, self.dv, self.r = n_heads, head_dim, v_head_dim, kv_rank
+        self.scale, self.eps, self.window = float(scale), float(eps), window
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        return [TensorSpec(f"{p}.q", (self.n_q * self.d, H), init="unit"),
+                TensorSpec(f"{p}.dkv", (self.r, H), init="unit"),
+                TensorSpec(f"{p}.dkv.norm", (self.r,), "vector", init="norm"),
+                TensorSpec(f"{p}.uk", (self.n_q * self.d, self.r), init="unit"),
+                TensorSpec(f"{p}.uv", (self.n_q * self.dv, self.r), init="unit"),
+                TensorSpec(f"{p}.o", (H, self.n_q * self.dv), init="unit")]
+
+    def kv_request(self) -> KVRequest:
+        return KVRequest(1, self.r, self.window, None, None, keys_only=True)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_in = torch.cat([tensors.pop(f"{p}.q"), tensors.pop(f"{p}.dkv")], dim=0).contiguous()     # [q | latent]
+        self.c_norm = tensors[f"{p}.dkv.norm"].float().contiguous()
+        # per head: U_h^T [kv_rank, head_dim] takes a query into the latent's basis; V_h [v_head_dim, kv_rank]
+        self.w_qc = tensors.pop(f"{p}.uk").view(self.n_q, self.d, self.r).transpose(1, 2).contiguous()
+        self.w_cv = tensors.pop(f"{p}.uv").view(self.n_q, self.dv, self.r).contiguous()
+        self.w_o = tensors[f"{p}.o"]
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_qc, self.w_cv, self.w_o))
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_in
+
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, ws, rt = ctx.T, ctx.ws, self.rt
+        proj = ws.get("lat_proj", (T, self.w_in.shape[0]), x.dtype)
+        matmul(x, self.w_in, None, proj, status=rt.status)
+        q = ws.get("lat_q", (T, self.n_q * self.d), x.dtype)
+        K.norm_append(proj, q, None, self.c_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, None,
+                      lc.group.table, 1, lc.writes, rt.status)
+        qc = ws.get("lat_qc", (T, self.n_q * self.r), x.dtype)
+        K.head_gemm(q, self.w_qc, qc)
+        ac = ws.get("lat_ac", (T, self.n_q * self.r), x.dtype)
+        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, 1, self.r, x.dtype, rt)
+        K.attention(qc, lc.k_pool, lc.k_pool, ac, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
+                    ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, 1, self.r, self.scale,
+                    self.window or 0, n_splits, split_len, scratch, rt.status)
+        v = ws.get("lat_v", (T, self.n_q * self.dv), x.dtype)
+        K.head_gemm(ac, self.w_cv, v)
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        return matmul(v, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)

@@ -107,6 +107,10 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu")
             t = 0.5 * t
         elif spec.init == "unit":
             t = t / (spec.shape[-1] ** 0.5)
+        elif spec.init == "lane_read":          # weights that read a mixture of lanes: about an average
+            t = 1.0 / spec.shape[0] + 0.1 * t
+        elif spec.init == "lane_mix":           # a lane mixing matrix: about the unit matrix
+            t = torch.eye(spec.shape[0], dtype=torch.float32, device=device) + 0.1 * t
         elif spec.init in ("normal", "bias", "embedding"):
             t = 0.02 * t
         else:
