@@ -28,7 +28,8 @@ above 15 % (testing/phase1.py:425-434).  The cache block is 16 tokens, as the
 benchmark configuration says; the library's own default of 64 is measured
 beside it (``points.decode_b8_block64``, ``points.prefill_block64_ms``).
 
-``--compare lonasun`` leaves all of that aside and measures the Lonasun design beside the Qwen2 dense decoder of the
+``--compare nizazen`` does the same for the Nizazen design (eight layers that alternate windowed and latent attention,
+dense and routed feed-forwards, on a residual stream of several lanes).  ``--compare lonasun`` leaves all of that aside and measures the Lonasun design beside the Qwen2 dense decoder of the
 same width, heads, layer runs and feed-forward work per token (random weights, a window as long as Lonasun's chunk):
 prefill and decode throughput of both at a few layer sizes, and for every mixer and feed-forward the device time of
 its kernels against the least time its operations and bytes need at the measured peaks.  It prints one JSON line of
@@ -317,6 +318,37 @@ def compare_configs(sz: dict):
     return lona, qwen
 
 
+NIZAZEN_SIZES = {
+    # width, heads, kv heads, head size, latent size, window, experts, choices, expert ff (choices x expert ff = the dense
+    # feed-forward's inner size), lanes
+    "w1024": dict(width=1024, heads=8, kv=2, dim=128, rank=256, window=1024, experts=16, top=4, ff=512, lanes=2),
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, rank=256, window=1024, experts=32, top=6, ff=768, lanes=2),
+    "w2048-d64": dict(width=2048, heads=32, kv=8, dim=64, rank=128, window=512, experts=64, top=8, ff=512, lanes=4),
+}
+
+
+def nizazen_configs(sz: dict):
+    """(Nizazen config dictionary, Qwen2 config dictionary) of equal width, heads, head size and layers: eight Nizazen
+    layers that alternate windowed and latent attention and dense and routed feed-forwards, beside eight dense layers
+    with the same window and a feed-forward of the operations per token of either of Nizazen's."""
+    att = {"dim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv"], "mask": {"size": sz["window"]},
+           "scale": sz["dim"] ** -0.5, "vdim": sz["dim"]}
+    lat = {"dim": sz["dim"], "heads": sz["heads"], "kv_rank": sz["rank"], "scale": sz["dim"] ** -0.5, "vdim": sz["dim"]}
+    inter = sz["top"] * sz["ff"]
+    dense = {"ff": inter, "kind": "dense"}
+    moe = {"expert": {"ff": sz["ff"], "limit": 7.0}, "kind": "moe", "router": {"experts": sz["experts"], "top": sz["top"]}}
+    kinds = [("latent_attention", lat, dense), ("attention", att, moe), ("attention", att, dense), ("latent_attention", lat, moe)]
+    niza = {"architecture": "Nizazen", "vocab": COMPARE_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+            "streams": sz["lanes"], "logit_softcap": 30.0,
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in kinds * 2]}
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "hidden_size": sz["width"],
+            "intermediate_size": inter, "num_hidden_layers": 8, "num_attention_heads": sz["heads"],
+            "num_key_value_heads": sz["kv"], "head_dim": sz["dim"], "vocab_size": COMPARE_VOCAB, "rms_norm_eps": 1e-5,
+            "rope_theta": 1000000.0, "max_position_embeddings": 8192, "tie_word_embeddings": False,
+            "use_sliding_window": True, "sliding_window": sz["window"], "max_window_layers": 0, "attention_bias": False}
+    return niza, qwen
+
+
 def compare_one(cfgd: dict, pk: dict, batch: int, context: int, prompt: int, steps: int, warmup: int, seed: int) -> dict:
     import torch
     from flashdecode_cuda_b200.config import config_from_dict
@@ -335,18 +367,23 @@ def compare_one(cfgd: dict, pk: dict, batch: int, context: int, prompt: int, ste
             times = timer_steps(timer, n_steps)
         T = sum(q_lens)
         need = {"mixer": 0.0, "feed_forward": 0.0}
+        by_class = {}                                      # the same per class of part, for designs whose layers differ
         for run in model.schedule:
             b = model.blocks[run.layer]
             fl, by = part_work(b.mixer, ctx_lens, q_lens)
             need["mixer"] += max(fl / tflops, by / gbs) * 1e3
+            by_class[type(b.mixer).__name__] = by_class.get(type(b.mixer).__name__, 0.0) + max(fl / tflops, by / gbs) * 1e3
             ff = b.feed_forward
+            if ff is None:
+                continue
             if type(ff).__name__ == "RoutedExperts":
                 share, touched = routing_of(model, T, ff.top, ff.E)
                 fl, by = part_work(ff, ctx_lens, q_lens, share, touched)
             else:
                 fl, by = part_work(ff, ctx_lens, q_lens)
             need["feed_forward"] += max(fl / tflops, by / gbs) * 1e3
-        res = {}
+            by_class[type(ff).__name__] = by_class.get(type(ff).__name__, 0.0) + max(fl / tflops, by / gbs) * 1e3
+        res = {"roofline_ms_by_class": {k: round(v, 4) for k, v in by_class.items()}}
         for label, kernels in times.items():
             ms = sum(v[0] for v in kernels.values())
             res[label] = {"ms": round(ms, 4), "kernels": {k: [round(v[0], 4), v[1]] for k, v in sorted(kernels.items())}}
@@ -419,21 +456,23 @@ def compare_main(args) -> int:
     clocks = ClockSampler()
     clocks.start()
     sizes = {}
-    for name in (args.compare_sizes.split(",") if args.compare_sizes else COMPARE_SIZES):
-        lona, qwen = compare_configs(COMPARE_SIZES[name])
-        entry = {"sizes": COMPARE_SIZES[name], "dense_intermediate": qwen["intermediate_size"]}
-        for key, cfgd in (("lonasun", lona), ("qwen2", qwen)):
+    design = args.compare
+    table = COMPARE_SIZES if design == "lonasun" else NIZAZEN_SIZES
+    for name in (args.compare_sizes.split(",") if args.compare_sizes else table):
+        ours, qwen = compare_configs(table[name]) if design == "lonasun" else nizazen_configs(table[name])
+        entry = {"sizes": table[name], "dense_intermediate": qwen["intermediate_size"]}
+        for key, cfgd in ((design, ours), ("qwen2", qwen)):
             entry[key] = compare_one(cfgd, pk, args.batch, 2048, 2048, min(args.steps, 64), max(3, args.warmup), args.seed)
             torch.cuda.empty_cache()
         entry["ratios"] = {
-            "prefill_tok_s": round(entry["lonasun"]["prefill"]["tok_s"] / entry["qwen2"]["prefill"]["tok_s"], 3),
-            "decode_tok_s": round(entry["lonasun"]["decode"]["tok_s"] / entry["qwen2"]["decode"]["tok_s"], 3)}
+            "prefill_tok_s": round(entry[design]["prefill"]["tok_s"] / entry["qwen2"]["prefill"]["tok_s"], 3),
+            "decode_tok_s": round(entry[design]["decode"]["tok_s"] / entry["qwen2"]["decode"]["tok_s"], 3)}
         for phase in ("prefill", "decode"):
             for part in ("mixer", "feed_forward"):
-                a, b = entry["lonasun"][phase]["parts"][part], entry["qwen2"][phase]["parts"][part]
+                a, b = entry[design][phase]["parts"][part], entry["qwen2"][phase]["parts"][part]
                 entry["ratios"][f"{phase}_{part}_frac"] = [a["frac"], b["frac"], round(a["frac"] / b["frac"], 3)]
         sizes[name] = entry
-    print(json.dumps({"compare": "lonasun", "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic: random weights",
+    print(json.dumps({"compare": design, "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic: random weights",
                       "peaks": pk, "batch": args.batch, "prompt": 2048, "context": 2048, "block_size": LIB_BLOCK_SIZE,
                       "clocks": clocks.stop(), "sizes": sizes}))
     return 0
@@ -649,7 +688,7 @@ def main() -> int:
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 point (slow at the larger presets)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the main run through the true 32-bit path (with --no-points)")
-    ap.add_argument("--compare", default="", choices=["", "lonasun"],
+    ap.add_argument("--compare", default="", choices=["", "lonasun", "nizazen"],
                     help="measure this design beside the closest dense model at equal sizes instead of the default run")
     ap.add_argument("--compare-sizes", default="", help="with --compare: names of the sizes to run, with commas (default: all)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],

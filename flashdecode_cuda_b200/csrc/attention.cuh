@@ -22,6 +22,10 @@ struct AttnParams {
     int* counters;             // [rows, n_kv] arrival counts for the in-kernel merge of the splits (all zero between launches), or null
     int max_blocks, num_blocks, block_size;
     int n_q, n_kv, G, d;
+    // The tensor-core decode kernel only: a group of more query heads than it takes is cut into kv_div smaller groups,
+    // each a key/value head of its own as far as the kernel's grid, rows and counters go (n_kv and G are then the
+    // numbers after the cut); the pool still has n_kv_pool heads per block and head kvh reads pool head kvh / kv_div.
+    int n_kv_pool, kv_div;
     int dv;                    // size of a value head (= d in the tensor-core kernels)
     int QT, n_splits, split_len, window;
     int chunk;                 // > 0: a query at position i sees key j <= i only if i / chunk == j / chunk

@@ -164,7 +164,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
                 // the usual case, a whole tile inside one block: one base address, constant offsets per lane
                 // (the address arithmetic of the general path below cost more than the tile's tensor work)
                 // the tile is DM_TILE * D contiguous elements in each pool: chunk c of the tile lies 16 c bytes in
-                const size_t base = (((size_t)tile_blk * p.n_kv + kvh) * bs + tile_off) * D + lane * 8;
+                const size_t base = (((size_t)tile_blk * p.n_kv_pool + kvh / p.kv_div) * bs + tile_off) * D + lane * 8;
                 const __nv_bfloat16* kb = kp + base;
                 const __nv_bfloat16* vb = vp + base;
                 const uint32_t ks32 = my_u32 + stage * 2 * TILE_BYTES, vs32 = ks32 + TILE_BYTES;
@@ -194,7 +194,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
                 if (blk < 0 || blk >= p.num_blocks) {
                     set_status(p.status, STATUS_BAD_BLOCK);
                 } else {
-                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + in_blk) * D + cc * 8;
+                    const size_t off = (((size_t)blk * p.n_kv_pool + kvh / p.kv_div) * bs + in_blk) * D + cc * 8;
                     ksrc = kp + off;
                     vsrc = vp + off;
                     bytes = 16;

@@ -340,6 +340,16 @@ typedef __nv_bfloat16 bf16;
 // Largest number of query tokens a CTA takes for a group size (0: unsupported).
 extern "C" int fd_attn_simt_qt(int G) { return G >= 1 && G <= RMAX ? (RMAX / G > 16 ? 16 : RMAX / G) : 0; }
 
+// Query heads per group the tensor-core decode kernel works on when a key/value head serves G of them: G itself up to
+// 16, else G's largest divisor up to 8 (the kernel's faster form), else up to 16; 0: the kernel does not take the sizes.
+extern "C" int fd_attn_decode_group(int G, int d, int dv) {
+    if (d != dv || (d != 64 && d != 128) || G < 1) return 0;
+    if (G <= 16) return G;
+    for (int g = 8; g >= 4; --g) if (G % g == 0) return g;
+    for (int g = 16; g >= 2; --g) if (G % g == 0) return g;
+    return 0;
+}
+
 // Floats of scratch the split form needs: part_acc [T, n_q, n_splits, d] (d: the size of a value head), then part_m
 // and part_l [T, n_q, n_splits].
 extern "C" long long fd_attn_scratch_floats(int T, int n_q, int d, int n_splits) {
@@ -389,6 +399,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.counters = nullptr;
     p.max_blocks = max_blocks; p.num_blocks = num_blocks; p.block_size = block_size;
     p.n_q = n_q; p.n_kv = n_kv; p.G = G; p.d = d; p.dv = dv; p.chunk = chunk;
+    p.n_kv_pool = n_kv; p.kv_div = 1;
     if (dv != d) use_mma = 0;          // the tensor-core kernels keep keys and values of one size
     int qt = fd_attn_simt_qt(G);
     if (qt > max_q_len) qt = max_q_len;
@@ -396,10 +407,12 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
 
     int rc = 1;
     if (use_mma && dtype == 1 && max_q_len == 1) {
-        p.counters = n_splits > 1 ? counters : nullptr;     // given: the kernel merges its own splits
-        rc = launch_attn_decode_mma(p, n_rows, stream);
-        if (rc == 0 && p.counters != nullptr) return 0;
-        p.counters = nullptr;
+        AttnParams pd = p;
+        const int cut = fd_attn_decode_group(G, d, dv);     // a large group as several smaller ones on the same pool head
+        if (cut > 0 && cut < G) { pd.G = cut; pd.kv_div = G / cut; pd.n_kv = n_kv * (G / cut); }
+        pd.counters = n_splits > 1 ? counters : nullptr;    // given: the kernel merges its own splits
+        rc = pd.n_kv <= 65535 ? launch_attn_decode_mma(pd, n_rows, stream) : 1;
+        if (rc == 0 && pd.counters != nullptr) return 0;
     }
     else if (use_mma && dtype == 1) {
         rc = use_mma == 2 ? 1 : launch_attn_prefill_tcgen05(p, n_rows, T, max_q_len, stream);

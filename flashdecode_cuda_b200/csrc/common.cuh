@@ -37,6 +37,23 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// What a gated feed-forward makes of a gate value g and an up value u in the products' epilogues (bfloat16 paths:
+// fast exponentials).  act 0: g sigmoid(g) u;  1: the tanh form of GELU of g, times u;  2: g' sigmoid(1.702 g') (u' + 1)
+// with g' = min(g, limit), u' = clamp(u, -limit, limit).
+__device__ __forceinline__ float gated_value(int act, float g, float u, float limit) {
+    if (act == 1) {
+        const float a = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float th = 1.f - __fdividef(2.f, __expf(2.f * a) + 1.f);        // tanh(a)
+        return 0.5f * g * (1.f + th) * u;
+    }
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+    }
+    return __fdividef(g, 1.f + __expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

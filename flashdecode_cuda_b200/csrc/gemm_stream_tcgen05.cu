@@ -58,6 +58,7 @@ struct GsParams {
     int M, N, K;
     int mode;              // 1: bf16 [M, N]; 2: float [M, N]; 3: gated, bf16 [M, N / 2]; 4: q/k/v (TcRope), out = q_out
     int bias_f32;
+    int act;               // mode 3: 0 SiLU, 1 tanh-form GELU (gated_value); a bias, if given, is added to gate and up
     int nx;                // M rounded up to a multiple of 16: the N of the MMAs
     int splits;            // CTAs of a cluster; each takes a range of K
     int stages;
@@ -196,11 +197,15 @@ __device__ __forceinline__ void gs_finish(const GsParams& p, const TcRope& ra, c
         if (p.mode == 3) {
             // 8 gate values, then the 8 up values of the same outputs (N is a multiple of 16)
             uint32_t o4[4];
+            if (p.bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float g0 = v[2 * j], g1 = v[2 * j + 1];
-                o4[j] = pack_bf16(__fdividef(g0, 1.f + __expf(-g0)) * v[8 + 2 * j], __fdividef(g1, 1.f + __expf(-g1)) * v[9 + 2 * j]);
+                for (int j = 0; j < 16; ++j)
+                    v[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[n_tile + j]
+                                       : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n_tile + j]);
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                o4[j] = pack_bf16(gated_value(p.act, v[2 * j], v[8 + 2 * j], 0.f), gated_value(p.act, v[2 * j + 1], v[9 + 2 * j], 0.f));
             *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * (p.N >> 1) + (n_tile >> 1)) =
                 make_uint4(o4[0], o4[1], o4[2], o4[3]);
             continue;
@@ -620,12 +625,15 @@ extern "C" int fd_gemm_stream_splits(int M, int N, int K) {
 extern "C" int fd_gemm_stream(const void* x, const void* w, const void* bias, int bias_f32, void* out, int mode,
                               int M, int N, int K, int splits, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    int act = 0;
+    if (mode == 6) { mode = 3; act = 1; }           // gated with the tanh form of GELU
     FD_REQUIRE(mode >= 1 && mode <= 3, -2, "gemm_stream: mode %d", mode);
     FD_REQUIRE(mode != 3 || N % 16 == 0, -2, "gemm_stream: the gated form needs N (= 2 x outputs) to be a multiple of 16, got %d", N);
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0, -2,
                "gemm_stream: x, W, bias and out must be 16-byte aligned");
     GsParams p = {};
     p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
+    p.act = act;
     TcRope ra = {};
     return launch_gs(x, w, p, ra, splits, stream, "gemm_stream");
 }

@@ -41,6 +41,8 @@ struct TcParams {
                            // 4: q/k/v projection with rotary encoding and cache append (TcRope);
                            // 5: bf16 [M, N] = max(x W^T, 0)^2
     int bias_f32;
+    int act = 0;           // mode 3: 0 SiLU, 1 tanh-form GELU, 2 clamped swish with `limit` (gated_value); a bias, if given,
+    float limit = 0.f;     // is added to gate and up
     unsigned long long wait_ns;   // limit of every bounded wait
     int skip_last;                // tests only: the producer leaves out its very last copy, so that a wait runs out
     // Grouped form (the persistent one-SM kernel only): W is a stack of matrices [E][N, K]; the 128-row tile t of x
@@ -170,10 +172,21 @@ __device__ __forceinline__ void tc_store32(const TcParams& p, const TcRope& ra, 
         for (int t = 0; t < 2; ++t)
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
-                const float g0 = __uint_as_float(v[t * 16 + j]), u0 = __uint_as_float(v[t * 16 + 8 + j]);
-                const float g1 = __uint_as_float(v[t * 16 + j + 1]), u1 = __uint_as_float(v[t * 16 + 9 + j]);
-                const __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0,
-                                                               g1 / (1.f + __expf(-g1)) * u1);
+                float g0 = __uint_as_float(v[t * 16 + j]), u0 = __uint_as_float(v[t * 16 + 8 + j]);
+                float g1 = __uint_as_float(v[t * 16 + j + 1]), u1 = __uint_as_float(v[t * 16 + 9 + j]);
+                if (p.bias != nullptr) {
+                    const int c = min(n + t * 16 + j, p.N - 10);
+                    if (p.bias_f32) {
+                        const float* b = static_cast<const float*>(p.bias) + c;
+                        g0 += b[0]; g1 += b[1]; u0 += b[8]; u1 += b[9];
+                    } else {
+                        const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + c;
+                        g0 += __bfloat162float(b[0]); g1 += __bfloat162float(b[1]);
+                        u0 += __bfloat162float(b[8]); u1 += __bfloat162float(b[9]);
+                    }
+                }
+                const __nv_bfloat162 r = __floats2bfloat162_rn(gated_value(p.act, g0, u0, p.limit),
+                                                               gated_value(p.act, g1, u1, p.limit));
                 packed[t * 4 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&r);
             }
         *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -741,12 +754,15 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
                           int M, int N, int K, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    int act = 0;
+    if (mode == 6) { mode = 3; act = 1; }           // gated with the tanh form of GELU
     FD_REQUIRE((mode >= 1 && mode <= 3) || mode == 5, -2, "gemm_tcgen05: mode %d", mode);
     FD_REQUIRE(mode != 3 || N % 16 == 0, -2, "gemm_tcgen05: the gated form needs N (= 2 x outputs) to be a multiple of 16, got %d", N);
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0, -2,
                "gemm_tcgen05: x, W and out must be 16-byte aligned");
     TcParams p;
     p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
+    p.act = act;
     p.wait_ns = g_tc_wait_ns; p.skip_last = g_tc_skip_last;
     TcRope ra = {};
     return launch_tc(x, w, p, ra, stream, "gemm_tcgen05");
@@ -756,11 +772,17 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
 // *n_row_tiles exist; tile t multiplies matrix tile_expert[t] of the stack w [E][N, K] (both on the device).
 // mode 5: out bf16 [M, N] = max(x w_e^T, 0)^2; mode 1: out bf16 [M, N]; mode 2: out float [M, N].  N >= 256 (the
 // persistent kernel).
+// mode 7: every matrix's rows in tiles of 8 gate + 8 up rows, out bf16 [M, N / 2] = the clamped swish of gate times
+// (up + 1) with `limit` (gated_value, act 2).
 extern "C" int fd_gemm_tc_grouped(const void* x, const void* w, void* out, int mode, int M, int N, int K, int E,
-                                  const int* tile_expert, const int* n_row_tiles, int* status, cudaStream_t stream) {
+                                  const int* tile_expert, const int* n_row_tiles, float limit, int* status,
+                                  cudaStream_t stream) {
     if (M == 0 || N == 0 || E == 0) return 0;
     FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
-    FD_REQUIRE(mode == 5 || mode == 2 || mode == 1, -2, "gemm_tcgen05 (grouped): mode %d", mode);
+    int act = 0;
+    if (mode == 7) { mode = 3; act = 2; }
+    FD_REQUIRE(mode == 5 || mode == 2 || mode == 1 || (mode == 3 && N % 32 == 0), -2,
+               "gemm_tcgen05 (grouped): mode %d (the gated form needs N, twice the outputs, to be a multiple of 32)", mode);
     FD_REQUIRE(M % TC_BM == 0 && N >= TW_BN && g_tc_wide != 0 && g_tc_wide != 2, -2,
                "gemm_tcgen05 (grouped): %d rows (whole tiles of %d) and %d columns (at least %d) on the persistent one-SM kernel",
                M, TC_BM, N, TW_BN);
@@ -770,6 +792,7 @@ extern "C" int fd_gemm_tc_grouped(const void* x, const void* w, void* out, int m
                "gemm_tcgen05: x, W and out must be 16-byte aligned");
     TcParams p;
     p.bias = nullptr; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = 0;
+    p.act = act; p.limit = limit;
     p.wait_ns = g_tc_wait_ns; p.skip_last = g_tc_skip_last;
     p.tile_expert = tile_expert; p.n_row_tiles = n_row_tiles;
     TcRope ra = {};

@@ -32,6 +32,7 @@ struct GemvParams {
     int mode;                    // 0: partial float [split, M, N]; 1: bf16 [M, N]; 2: float [M, N]; 3: gated bf16 [M, N / 2];
                                  // 4: q/k/v projection with rotary encoding and cache append (see RopeArgs)
     int bias_f32;
+    int act;                     // mode 3: 0 SiLU, 1 tanh-form GELU (gated_value); a bias, if given, is added to gate and up
     // Memory that a later kernel will stream (for the q/k/v projection the output projection's weights, which are
     // read after the attention; for a block's last product the next block's first weights), or null: each CTA asks
     // L2 for its share once its own loads are through, so that HBM goes on delivering through this kernel's tail and
@@ -164,14 +165,20 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const RopeArg
         const int NO = p.N >> 1;
         if (o < NO) {
             __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+            float bg = 0.f, bu = 0.f;
+            if (p.bias != nullptr) {
+                const int ng = tile * 16 + r;
+                bg = p.bias_f32 ? static_cast<const float*>(p.bias)[ng] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[ng]);
+                bu = p.bias_f32 ? static_cast<const float*>(p.bias)[ng + 8] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[ng + 8]);
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int m = nt * 8 + q * 2 + e;
                     if (m < p.M) {
-                        const float g = acc[nt][e], u = acc[nt][2 + e];
-                        out[(size_t)m * NO + o] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+                        const float g = acc[nt][e] + bg, u = acc[nt][2 + e] + bu;
+                        out[(size_t)m * NO + o] = __float2bfloat16_rn(gated_value(p.act, g, u, 0.f));
                     }
                 }
         }

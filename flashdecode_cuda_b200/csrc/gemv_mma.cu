@@ -287,6 +287,8 @@ extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_
     FD_REQUIRE((uintptr_t)prefetch % 16 == 0, -2, "gemv: the memory to prefetch must be 16-byte aligned");
     FD_REQUIRE(M >= 1 && M <= 64, -2, "gemv: %d rows of x; this kernel takes 1..64", M);
     FD_REQUIRE(K >= 32 && K % 32 == 0, -2, "gemv: K=%d must be a positive multiple of 32", K);
+    int act = 0;
+    if (mode == 6) { mode = 3; act = 1; }           // gated with the tanh form of GELU
     FD_REQUIRE(n_splits >= 1 && (mode != 3 || n_splits == 1), -2, "gemv: the gated form cannot be split over K");
     FD_REQUIRE(mode == 0 || n_splits <= 8, -2, "gemv: at most 8 splits add up inside a cluster, got %d", n_splits);
     FD_REQUIRE(mode >= 0 && mode <= 3, -2, "gemv: mode %d", mode);
@@ -294,7 +296,7 @@ extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, -2, "gemv: x and W must be 16-byte aligned");
     GemvParams p;
     p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = out;
-    p.M = M; p.N = N; p.K = K; p.n_splits = n_splits; p.mode = mode; p.bias_f32 = bias_f32;
+    p.M = M; p.N = N; p.K = K; p.n_splits = n_splits; p.mode = mode; p.bias_f32 = bias_f32; p.act = act;
     p.pf_ptr = (const unsigned char*)prefetch; p.pf_bytes = prefetch ? prefetch_bytes : 0;
     RopeArgs ra = {};
     return run_gemv(p, ra, stream);
@@ -321,7 +323,7 @@ extern "C" int fd_gemv_qkv_rope(const void* x, const void* w, const void* bias, 
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, -2, "gemv: x and W must be 16-byte aligned");
     GemvParams p;
     p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = q_out;
-    p.M = M; p.N = (n_q + 2 * n_kv) * d; p.K = K; p.n_splits = n_splits; p.mode = 4; p.bias_f32 = bias_f32;
+    p.M = M; p.N = (n_q + 2 * n_kv) * d; p.K = K; p.n_splits = n_splits; p.mode = 4; p.bias_f32 = bias_f32; p.act = 0;
     p.pf_ptr = (const unsigned char*)prefetch; p.pf_bytes = prefetch ? prefetch_bytes : 0;
     RopeArgs ra;
     ra.cos_t = cos_t; ra.sin_t = sin_t; ra.tok_row = tok_row; ra.tok_pos = tok_pos; ra.row_slot = row_slot;

@@ -61,6 +61,47 @@ head_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, T* __restrict
     }
 }
 
+// Steps of few rows in bfloat16 (K a multiple of 8): a warp per output column (head, n) reads that row of w once in
+// 16-byte pieces and takes it against every row of a; eight warps per CTA.
+template <int MAXT>
+__global__ void __launch_bounds__(256)
+head_gemv_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                 int T_rows, int heads, int N, int K) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * 8 + warp;
+    if (col >= heads * N) return;
+    const int h = col / N;
+    const __nv_bfloat16* wr = w + (size_t)col * K;
+    const __nv_bfloat16* ah = a + (size_t)h * K;
+    const size_t lda = (size_t)heads * K;
+    float acc[MAXT];
+#pragma unroll
+    for (int t = 0; t < MAXT; ++t) acc[t] = 0.f;
+    for (int c = lane * 8; c < K; c += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(wr + c);
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int t = 0; t < MAXT; ++t) {
+            if (t < T_rows) {
+                const uint4 av = *reinterpret_cast<const uint4*>(ah + t * lda + c);
+                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    acc[t] = fmaf(__low2float(w2[e]), __low2float(a2[e]), acc[t]);
+                    acc[t] = fmaf(__high2float(w2[e]), __high2float(a2[e]), acc[t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < MAXT; ++t) {
+        if (t < T_rows) {
+            const float v = warp_sum(acc[t]);
+            if (lane == 0) out[(size_t)t * heads * N + col] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
 }  // namespace fd
 
 using namespace fd;
@@ -69,6 +110,14 @@ extern "C" int fd_head_gemm(const void* a, const void* w, void* out, int dtype, 
                             cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(heads > 0 && heads <= 65535 && N > 0 && K > 0, -2, "head_gemm: %d heads, N %d, K %d", heads, N, K);
+    if (dtype == 1 && T <= 16 && K % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0) {
+        const dim3 g((unsigned)((heads * (long long)N + 7) / 8));
+        if (T <= 8)
+            return launch("head_gemm", head_gemv_kernel<8>, g, dim3(256), 0, stream, dim3(1, 1, 1), (const __nv_bfloat16*)a,
+                          (const __nv_bfloat16*)w, (__nv_bfloat16*)out, T, heads, N, K);
+        return launch("head_gemm", head_gemv_kernel<16>, g, dim3(256), 0, stream, dim3(1, 1, 1), (const __nv_bfloat16*)a,
+                      (const __nv_bfloat16*)w, (__nv_bfloat16*)out, T, heads, N, K);
+    }
     dim3 grid((N + HG_NT - 1) / HG_NT, (T + HG_MT - 1) / HG_MT, heads);
     FD_REQUIRE(grid.y <= 65535, -2, "head_gemm: %d rows are too many", T);
     if (dtype == 0)

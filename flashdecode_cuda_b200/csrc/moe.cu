@@ -161,11 +161,13 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int*
 // MODE 0: a[row] = x[sorted_pair[row] / top], out = relu(acc)^2 as T into act [cap, N]
 // MODE 1: a[row] = act[row],                  out = acc as T into y [cap, N]
 // MODE 2: a[row] = x[sorted_pair[row] / top], out = acc as T into [cap, N] (an activation kernel follows)
+// MODE 3: a[row] = x[sorted_pair[row] / top], w rows in tiles of 8 gate + 8 up rows, out [cap, N / 2] =
+//         gated_value(act 2: clamped swish with `limit`) of each gate / up pair
 template <typename T, int MODE>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restrict__ out,
                 const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
-                const int* __restrict__ n_tiles, int top, int N, int K) {
+                const int* __restrict__ n_tiles, int top, int N, int K, float limit) {
     const int tile = blockIdx.y;
     if (tile >= *n_tiles) return;
     __shared__ float a_s[MOE_MT][MOE_KT + 1];
@@ -205,6 +207,20 @@ moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restri
         }
         __syncthreads();
     }
+    if (MODE == 3) {
+        // a tile of 16 columns is 8 gate + 8 up values: the thread 8 columns on holds this thread's partner
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, acc[i][j], 8);
+                const int r = 2 * ty + i, c = n0 + 16 * j + tx;
+                if (tx < 8 && row_s[r] >= 0 && c + 8 < N)
+                    static_cast<T*>(out)[(size_t)(tile * MOE_MT + r) * (N >> 1) + ((n0 + 16 * j) >> 1) + tx] =
+                        from_float<T>(gated_value(2, acc[i][j], other, limit));
+            }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = 2 * ty + i;
@@ -231,7 +247,7 @@ template <int BM, int BN, int WM, int WN, int MODE>
 __global__ void __launch_bounds__(WM * WN * 32)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
-                    const int* __restrict__ n_tiles, int top, int N, int K) {
+                    const int* __restrict__ n_tiles, int top, int N, int K, float limit) {
     constexpr int THREADS = WM * WN * 32, BK = 64, STAGES = 3;
     constexpr int TM = BM / WM, TN = BN / WN, MI = TM / 16, NI = TN / 8;
     static_assert(TM % 16 == 0 && TN % 16 == 0, "a warp takes whole 16 x 16 parts");
@@ -314,6 +330,19 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
         for (int hh = 0; hh < 2; ++hh) {
             const int r = wm * TM + i * 16 + (lane >> 2) + hh * 8;
             if (row_s[r] < 0) continue;
+            if (MODE == 3) {
+                // columns j * 8 .. of even j are gate values, those of j + 1 the up values of the same outputs
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out) + (size_t)(tile * BM + r) * (N >> 1);
+#pragma unroll
+                for (int j = 0; j < NI; j += 2) {
+                    const int cg = n0 + wn * TN + j * 8;
+                    if (cg + 16 > N) continue;
+                    *reinterpret_cast<__nv_bfloat162*>(o + (cg >> 1) + (lane & 3) * 2) =
+                        __floats2bfloat162_rn(gated_value(2, acc[i][j][hh * 2], acc[i][j + 1][hh * 2], limit),
+                                              gated_value(2, acc[i][j][hh * 2 + 1], acc[i][j + 1][hh * 2 + 1], limit));
+                }
+                continue;
+            }
             const size_t orow = (size_t)(tile * BM + r) * N;
 #pragma unroll
             for (int j = 0; j < NI; ++j) {
@@ -334,7 +363,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
 
 template <int BM, int BN, int WM, int WN, int MODE>
 static int launch_moe_mma(const void* a, const void* w, void* out, const int* sorted_pair, const int* tile_expert,
-                          const int* n_tiles, int cap, int top, int N, int K, cudaStream_t stream) {
+                          const int* n_tiles, int cap, int top, int N, int K, float limit, cudaStream_t stream) {
     auto k = moe_gemm_mma_kernel<BM, BN, WM, WN, MODE>;
     const size_t smem = (size_t)3 * (BM + BN) * 64 * 2 + BM * sizeof(int);
     static bool configured = false;
@@ -346,7 +375,7 @@ static int launch_moe_mma(const void* a, const void* w, void* out, const int* so
     dim3 grid((N + BN - 1) / BN, cap / BM);
     FD_REQUIRE(grid.y <= 65535, -2, "moe_gemm: %d row tiles are too many", (int)grid.y);
     return launch("moe_gemm", k, grid, dim3(WM * WN * 32), smem, stream, dim3(1, 1, 1), (const __nv_bfloat16*)a,
-                  (const __nv_bfloat16*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K);
+                  (const __nv_bfloat16*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K, limit);
 }
 
 // xs[row] = x[sorted_pair[row] / top] for the grouped rows that exist, zeros for the padding rows among them: the
@@ -474,21 +503,25 @@ extern "C" int fd_moe_align(const int* ids, int P, int E, int* pair_pos, int* so
 // mode 2: a = x [T, K], out [cap, N] (dtype) = x W_e^T.
 // w [E, N, K].
 // mt: the tile rows the grouping was made with.
+// mode 3: a = x [T, K], w rows in tiles of 8 gate + 8 up, out [cap, N / 2] = clamped swish of gate times (up + 1).
 extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, int mode, const int* sorted_pair,
                            const int* tile_expert, const int* n_tiles, int cap, int mt, int top, int N, int K,
-                           cudaStream_t stream) {
+                           float limit, cudaStream_t stream) {
     if (cap == 0) return 0;
-    FD_REQUIRE(cap % mt == 0 && N > 0 && K > 0 && mode >= 0 && mode <= 2, -2, "moe_gemm: bad sizes or mode");
+    FD_REQUIRE(cap % mt == 0 && N > 0 && K > 0 && mode >= 0 && mode <= 3 && (mode != 3 || N % 16 == 0), -2,
+               "moe_gemm: bad sizes or mode (the gated form needs N, twice the outputs, to be a multiple of 16)");
     if (dtype == 1 && K % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0) {
         if (mt == 128) {
-            if (mode == 0) return launch_moe_mma<128, 128, 2, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
-            if (mode == 2) return launch_moe_mma<128, 128, 2, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
-            return launch_moe_mma<128, 128, 2, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+            if (mode == 0) return launch_moe_mma<128, 128, 2, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            if (mode == 2) return launch_moe_mma<128, 128, 2, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            if (mode == 3) return launch_moe_mma<128, 128, 2, 4, 3>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            return launch_moe_mma<128, 128, 2, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
         }
         if (mt == 32) {
-            if (mode == 0) return launch_moe_mma<32, 64, 1, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
-            if (mode == 2) return launch_moe_mma<32, 64, 1, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
-            return launch_moe_mma<32, 64, 1, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, stream);
+            if (mode == 0) return launch_moe_mma<32, 64, 1, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            if (mode == 2) return launch_moe_mma<32, 64, 1, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            if (mode == 3) return launch_moe_mma<32, 64, 1, 4, 3>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            return launch_moe_mma<32, 64, 1, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
         }
     }
     FD_REQUIRE(mt == MOE_MT, -2, "moe_gemm: the CUDA-core product takes tiles of %d rows, not %d", MOE_MT, mt);
@@ -496,10 +529,11 @@ extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, i
     FD_REQUIRE(grid.y <= 65535, -2, "moe_gemm: %d row tiles are too many", (int)grid.y);
 #define FD_MG(T_, M_)                                                                                                \
     return launch("moe_gemm", moe_gemm_kernel<T_, M_>, grid, dim3(MOE_THREADS), 0, stream, dim3(1, 1, 1), (const T_*)a, \
-                  (const T_*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K)
-    if (dtype == 0) { if (mode == 0) FD_MG(float, 0); if (mode == 2) FD_MG(float, 2); FD_MG(float, 1); }
+                  (const T_*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K, limit)
+    if (dtype == 0) { if (mode == 0) FD_MG(float, 0); if (mode == 2) FD_MG(float, 2); if (mode == 3) FD_MG(float, 3); FD_MG(float, 1); }
     if (mode == 0) FD_MG(bf16, 0);
     if (mode == 2) FD_MG(bf16, 2);
+    if (mode == 3) FD_MG(bf16, 3);
     FD_MG(bf16, 1);
 #undef FD_MG
 }

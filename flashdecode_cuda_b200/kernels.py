@@ -92,6 +92,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P, c_ulonglong, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
         "fd_attn_simt_qt": [I],
+        "fd_attn_decode_group": [I, I, I],
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P],
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P],
@@ -110,10 +111,10 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_norm_append": [P, I, P, I, P, P, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "fd_head_gemm": [P, P, P, I, I, I, I, I, P],
         "fd_moe_align": [P, I, I, P, P, P, P, I, I, P],
-        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, P],
+        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, F, P],
         "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
         "fd_moe_gather": [P, P, P, P, I, I, I, I, P],
-        "fd_gemm_tc_grouped": [P, P, P, I, I, I, I, I, P, P, P, P],
+        "fd_gemm_tc_grouped": [P, P, P, I, I, I, I, I, P, P, F, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
         "fd_copy_d2h_sync": [P, P, LL, P],
@@ -326,12 +327,20 @@ def norm_append(proj: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torc
                                 int(write_kv), _ptr(status), _stream()))
 
 
+HEAD_GEMM_LIBRARY_ROWS = 64      # from this many rows on, the per-head products of bfloat16 steps go to the library's batched product
+
+
 def head_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, h, :] = w[h] a[t, h, :]: a [T, heads * K], w [heads, N, K], out [T, heads * N]; float accumulation."""
+    """out[t, h, :] = w[h] a[t, h, :]: a [T, heads * K], w [heads, N, K], out [T, heads * N]; float accumulation.
+    float32: the library's own CUDA-core kernel with k ascending (no bit of a row depends on the step's other rows);
+    bfloat16: a warp per output column for steps of up to 16 rows, cuBLAS's strided batched product for prompts."""
     heads, N, Kd = w.shape
     T = a.shape[0]
     assert a.shape == (T, heads * Kd) and out.shape == (T, heads * N) and a.dtype == w.dtype == out.dtype
     assert a.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    if a.dtype == torch.bfloat16 and T >= HEAD_GEMM_LIBRARY_ROWS:
+        torch.bmm(a.view(T, heads, Kd).transpose(0, 1), w.transpose(1, 2), out=out.view(T, heads, N).transpose(0, 1))
+        return
     _check(lib().fd_head_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), T, heads, N, Kd, _stream()))
 
 
@@ -382,6 +391,7 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
 
 
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
+GEMV_GATED_GELU = 6      # gated with the tanh form of GELU instead of SiLU; both take a bias on gate and up
 
 
 def gemm_tc_set_wide(on) -> None:
@@ -444,8 +454,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     N = w.shape[0]
     assert x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K
     if gated:
-        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and bias is None
-        mode = GEMV_GATED
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2)
+        mode = GEMV_GATED_GELU if gated == "gelu_tanh" else GEMV_GATED
     elif relu2:
         assert out.dtype == torch.bfloat16 and out.shape == (M, N)
         mode = GEMM_RELU2
@@ -472,8 +482,8 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     N = w.shape[0]
     assert x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K
     if gated:
-        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and bias is None
-        mode = GEMV_GATED
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2)
+        mode = GEMV_GATED_GELU if gated == "gelu_tanh" else GEMV_GATED
     else:
         assert out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
         mode = GEMV_BF16 if out.dtype == torch.bfloat16 else GEMV_F32
@@ -550,7 +560,8 @@ def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     want = {GEMV_PARTIAL: (torch.float32, n_splits * M * N), GEMV_BF16: (torch.bfloat16, M * N),
-            GEMV_F32: (torch.float32, M * N), GEMV_GATED: (torch.bfloat16, M * N // 2)}[mode]
+            GEMV_F32: (torch.float32, M * N), GEMV_GATED: (torch.bfloat16, M * N // 2),
+            GEMV_GATED_GELU: (torch.bfloat16, M * N // 2)}[mode]
     assert out.dtype == want[0] and out.numel() == want[1], (out.dtype, out.shape, mode)
     _check(lib().fd_gemv(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
                          _ptr(out), mode, M, N, K, n_splits, *_prefetch_args(prefetch, prefetch_bytes), _stream()))
@@ -563,6 +574,13 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     assert w.shape[1] == K and out.shape == (M, N) and w.dtype == x.dtype
     _check(lib().fd_gemm_simt(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _dt(x.dtype),
                               _dt(bias.dtype) if bias is not None else 0, _dt(out.dtype), M, N, K, _stream()))
+
+
+def attention_decode_heads(n_q: int, n_kv: int, head_dim: int, v_dim: int) -> int:
+    """Key/value heads as the tensor-core decode kernel counts them: a group of more than 16 query heads on one
+    key/value head is cut into several smaller groups that read the same cached head."""
+    g = int(lib().fd_attn_decode_group(n_q // n_kv, head_dim, v_dim))
+    return n_q // g if g > 0 else n_kv
 
 
 def attention_scratch_floats(n_tokens: int, n_q: int, head_dim: int, n_splits: int) -> int:
@@ -596,7 +614,8 @@ def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, 
             int(chunk), n_splits, split_len, _ptr(scratch)]
     if fn_name != "fd_attention_simt":
         fused = n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16
-        args.append(_ptr(_counters(q.device, n_rows * n_kv)) if fused else None)
+        # (a large group of query heads may be cut into several: at most one counter per query head)
+        args.append(_ptr(_counters(q.device, n_rows * n_q)) if fused else None)
     args.append(_ptr(status))
     if fn_name == "fd_attention":
         args += list(_prefetch_args(prefetch, prefetch_bytes))
@@ -768,7 +787,8 @@ def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, sorted_pair: torch.Tensor,
-             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int, plain: bool = False) -> None:
+             tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int, plain: bool = False,
+             gated_limit: Optional[float] = None) -> None:
     """Grouped product with the experts' stacked matrices w [E, N, K].  ``down`` False: a = x [T, K] (rows gathered
     through the grouping), out [cap, N] = relu(x w_e^T)^2 in a's dtype; True: a = the grouped activations [cap, K],
     out [cap, N] in a's dtype.  ``plain`` (with ``down`` False): no activation, out = x w_e^T (a gated activation follows
@@ -776,10 +796,12 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, so
     the tensor cores, everything else on the CUDA cores (tiles of 32 rows only)."""
     E, N, Kd = w.shape
     cap = sorted_pair.numel()
-    assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N)
-    assert out.dtype == a.dtype and (not down or a.shape[0] == cap)
-    _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), 1 if down else (2 if plain else 0), _ptr(sorted_pair), _ptr(tile_expert),
-                             _ptr(n_tiles), cap, mt, top, N, Kd, _stream()))
+    gated = gated_limit is not None       # w rows in tiles of 8 gate + 8 up: out [cap, N / 2] = clamped swish(gate) (up + 1)
+    assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N // 2 if gated else N)
+    assert out.dtype == a.dtype and (not down or a.shape[0] == cap) and not (gated and (down or plain))
+    mode = 1 if down else (3 if gated else (2 if plain else 0))
+    _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), mode, _ptr(sorted_pair), _ptr(tile_expert),
+                             _ptr(n_tiles), cap, mt, top, N, Kd, float(gated_limit or 0.0), _stream()))
 
 
 def moe_gather(x: torch.Tensor, xs: torch.Tensor, sorted_pair: torch.Tensor, n_tiles: torch.Tensor, top: int,
@@ -797,17 +819,20 @@ def gemm_tc_grouped_supported(N: int, K: int) -> bool:
 
 
 def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, relu2: bool, tile_expert: torch.Tensor,
-                    n_tiles: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+                    n_tiles: torch.Tensor, status: Optional[torch.Tensor] = None,
+                    gated_limit: Optional[float] = None) -> None:
     """Grouped product on the tcgen05 tensor cores: x [cap, K] in row tiles of 128 of which the first ``n_tiles``
     exist, tile t times matrix ``tile_expert[t]`` of the stack w [E, N, K] (both device tensors).  ``relu2``: out
     bfloat16 [cap, N] = max(x w_e^T, 0)^2; else out bfloat16 or float32 [cap, N]."""
     cap, Kd = x.shape
     E, N, _ = w.shape
-    assert x.dtype == w.dtype == torch.bfloat16 and w.shape[2] == Kd and out.shape == (cap, N) and cap % 128 == 0
-    assert out.dtype in ((torch.bfloat16,) if relu2 else (torch.bfloat16, torch.float32)) and tile_expert.numel() * 128 >= cap
-    mode = 5 if relu2 else (1 if out.dtype == torch.bfloat16 else 2)
+    gated = gated_limit is not None   # w rows in tiles of 8 gate + 8 up: out bfloat16 [cap, N / 2] = clamped swish(gate) (up + 1)
+    assert x.dtype == w.dtype == torch.bfloat16 and w.shape[2] == Kd and cap % 128 == 0
+    assert out.shape == (cap, N // 2 if gated else N) and not (gated and relu2)
+    assert out.dtype in ((torch.bfloat16,) if relu2 or gated else (torch.bfloat16, torch.float32)) and tile_expert.numel() * 128 >= cap
+    mode = 7 if gated else (5 if relu2 else (1 if out.dtype == torch.bfloat16 else 2))
     _check(lib().fd_gemm_tc_grouped(_ptr(x), _ptr(w), _ptr(out), mode, cap, N, Kd, E, _ptr(tile_expert),
-                                    _ptr(n_tiles), _ptr(status), _stream()))
+                                    _ptr(n_tiles), float(gated_limit or 0.0), _ptr(status), _stream()))
 
 
 def moe_combine(y: Optional[torch.Tensor], x: torch.Tensor, shared: Optional[torch.Tensor], ids: torch.Tensor,

@@ -20,7 +20,7 @@ from . import kernels as K
 LAUNCHERS = ["embed", "add_rmsnorm", "silu_mul", "rope_append", "gemv_qkv_rope", "gemm_tc_qkv_rope", "gemm_tc",
              "gemm_stream", "gemm_stream_qkv_rope", "gemv", "gemm_simt", "attention", "conv_rope_append",
              "conv_state_update", "gate_mul", "add_concat", "relu2", "moe_route", "moe_align", "moe_gemm", "moe_combine",
-             "moe_gather", "gemm_tc_grouped"]
+             "moe_gather", "gemm_tc_grouped", "glu_mul", "softcap", "lanes_norm", "lanes_fill", "norm_append", "head_gemm"]
 
 
 class PartTimer:
@@ -148,14 +148,31 @@ def part_work(part, ctx_lens: Sequence[int], q_lens: Sequence[int], real_choice_
         flops = 2 * T * H * part.w_in.shape[0] + 2 * T * n_q * dv * H + 2 * n_q * (d + dv) * pairs
         kv = keys_read(ctx_lens, q_lens, part.window, part.chunk) * n_kv * (d + dv) * el
         return float(flops), float(part.weight_bytes() + kv + act)
-    if name == "SwiGLU":
+    if name == "QKNormedAttention":
+        n_q, n_kv, d, dv = part.n_q, part.n_kv, part.d, part.dv
+        pairs = visible_pairs(ctx_lens, q_lens, part.window, None)
+        flops = 2 * T * H * part.w_in.shape[0] + 2 * T * n_q * dv * H + 2 * n_q * (d + dv) * pairs
+        kv = keys_read(ctx_lens, q_lens, part.window, None) * n_kv * (d + dv) * el
+        return float(flops), float(part.weight_bytes() + kv + act)
+    if name == "LatentAttention":
+        # the cheaper of attending in the latent's basis (what the part does) and expanding every visible position's
+        # keys and values first (what a prompt without a cache could do)
+        n_q, d, dv, r = part.n_q, part.d, part.dv, part.r
+        pairs = visible_pairs(ctx_lens, q_lens, part.window, None)
+        n_keys = keys_read(ctx_lens, q_lens, part.window, None)
+        common = 2 * T * H * (n_q * d + r) + 2 * T * n_q * dv * H
+        latent = 2 * T * n_q * r * (d + dv) + 4 * n_q * r * pairs
+        expanded = 2 * n_keys * r * n_q * (d + dv) + 2 * n_q * (d + dv) * pairs
+        return float(common + min(latent, expanded)), float(part.weight_bytes() + n_keys * r * el + act)
+    if name in ("SwiGLU", "GatedMLP"):
         return float(2 * T * 3 * H * part.inter), float(part.weight_bytes() + act)
     if name == "RoutedExperts":
         sff = part.shared_ff or 0
-        flops = 2 * T * H * (part.E + part.n_identity) + 2 * T * part.top * real_choice_share * 2 * H * part.ff \
+        mats = 3 if getattr(part, "gated", False) else 2          # matrices of an expert
+        flops = 2 * T * H * (part.E + part.n_identity) + 2 * T * part.top * real_choice_share * mats * H * part.ff \
             + 2 * T * 2 * H * sff
         touched = part.E if experts_touched is None else experts_touched
-        byt = (part.E + part.n_identity) * H * el + 2 * H * sff * el + touched * 2 * H * part.ff * el + act
+        byt = (part.E + part.n_identity) * H * el + 2 * H * sff * el + touched * mats * H * part.ff * el + act
         return float(flops), float(byt)
     raise ValueError(f"no work model for a {name}")
 

@@ -82,7 +82,8 @@ class GatedMLP(FeedForward):
     ``activation``: ``"silu"`` or ``"gelu_tanh"`` (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))).  ``bias``: every
     projection has one.  Tensors ``<prefix>.gate`` / ``.up`` / ``.down`` (stored [out, in]) and, with biases,
     ``.gate.b`` / ``.up.b`` / ``.down.b``.  gate and up are one packed product; the activation is computed in float32
-    from the product's output and rounded once.
+    from the product's float sums (bfloat16: in the product's epilogue, rows of the packed matrix in tiles of 8 gate +
+    8 up) or from its output (float32) and rounded once.
     """
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh",
@@ -106,11 +107,20 @@ class GatedMLP(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         p = self.prefix
-        self.w_gate_up = torch.cat([tensors.pop(f"{p}.gate"), tensors.pop(f"{p}.up")], dim=0).contiguous()
+        I = self.inter
+        # bfloat16: tiles of 16 rows, 8 gate rows and the 8 up rows of the same outputs, so that the thread of a product's
+        # epilogue that holds gate_i also holds up_i
+        self.tiled = rt.dtype == torch.bfloat16 and I % 8 == 0
+
+        def pack(g, u):
+            if not self.tiled:
+                return torch.cat([g, u], dim=0).contiguous()
+            return torch.stack([g.reshape(I // 8, 8, -1), u.reshape(I // 8, 8, -1)], dim=1).reshape(2 * I, *g.shape[1:]).contiguous()
+        self.w_gate_up = pack(tensors.pop(f"{p}.gate"), tensors.pop(f"{p}.up"))
         self.w_down = tensors[f"{p}.down"]
         self.b_gate_up = self.b_down = None
         if self.bias:
-            self.b_gate_up = torch.cat([tensors.pop(f"{p}.gate.b"), tensors.pop(f"{p}.up.b")]).contiguous()
+            self.b_gate_up = pack(tensors.pop(f"{p}.gate.b"), tensors.pop(f"{p}.up.b"))
             self.b_down = tensors[f"{p}.down.b"]
 
     def weight_bytes(self) -> int:
@@ -121,10 +131,18 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx, x: torch.Tensor, parts_ok: bool = False) -> torch.Tensor:
         T, ws = ctx.T, ctx.ws
-        gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
-        matmul(x, self.w_gate_up, self.b_gate_up, gu, status=self.rt.status)
         act = ws.get("ffn_act", (T, self.inter), x.dtype)
-        K.glu_mul(gu, act, self.kind)
+        N2, H = 2 * self.inter, self.hidden_size
+        if self.tiled and T <= GEMV_MAX_ROWS and K.gemv_splits(T, N2, H, 1, allow_split=False) == 1:
+            K.gemv(x, self.w_gate_up, self.b_gate_up, act, K.GEMV_GATED_GELU if self.kind else K.GEMV_GATED)
+        elif self.tiled and stream_gemm(T, N2, H):
+            K.gemm_stream(x, self.w_gate_up, self.b_gate_up, act, gated=self.activation, status=self.rt.status)
+        elif self.tiled and fused_prompt_gemm(T, N2, H):
+            K.gemm_tc(x, self.w_gate_up, self.b_gate_up, act, gated=self.activation, status=self.rt.status)
+        else:
+            gu = ws.get("gate_up", (T, N2), x.dtype)
+            matmul(x, self.w_gate_up, self.b_gate_up, gu, status=self.rt.status)
+            K.glu_mul(gu, act, self.kind, tiled=self.tiled)
         out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
         return matmul(act, self.w_down, self.b_down, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status,
                       upcoming=ctx.upcoming)

@@ -77,8 +77,17 @@ class RoutedExperts(FeedForward):
         self.rt = rt
         p = self.prefix
         if self.E:
-            if self.gated:       # [E, 2 ff, H]: an expert's gate rows, then its up rows: one product
-                self.w_up = torch.stack([torch.cat([tensors.pop(f"{p}.e{e}.gate"), tensors.pop(f"{p}.e{e}.up")])
+            if self.gated:
+                # [E, 2 ff, H]: one product for an expert's gate and up rows.  bfloat16: in tiles of 8 gate rows + the 8 up
+                # rows of the same outputs, for the products' gated epilogues; float32: gate rows, then up rows
+                self.tiled = rt.dtype == torch.bfloat16 and self.ff % 8 == 0
+                f8 = self.ff // 8
+
+                def pack(g, u):
+                    if not self.tiled:
+                        return torch.cat([g, u])
+                    return torch.stack([g.view(f8, 8, -1), u.view(f8, 8, -1)], dim=1).reshape(2 * self.ff, -1)
+                self.w_up = torch.stack([pack(tensors.pop(f"{p}.e{e}.gate"), tensors.pop(f"{p}.e{e}.up"))
                                          for e in range(self.E)]).contiguous()
             else:
                 self.w_up = torch.stack([tensors.pop(f"{p}.e{e}.up") for e in range(self.E)]).contiguous()   # [E, ff, H]
@@ -142,20 +151,26 @@ class RoutedExperts(FeedForward):
             act = ws.get("moe_act", (cap, self.ff), x.dtype)
             y = ws.get("moe_y", (cap, H), x.dtype)
             n_up = self.w_up.shape[1]                   # ff, or 2 ff for gated experts
-            gu = ws.get("moe_gu", (cap, n_up), x.dtype) if self.gated else None
+            fused = self.gated and self.tiled           # the gated activation in the up product's epilogue
+            gu = ws.get("moe_gu", (cap, n_up), x.dtype) if self.gated and not fused else None
             if (mt == 128 and GROUPED_GEMM == "auto" and K.gemm_tc_grouped_supported(n_up, H)
                     and K.gemm_tc_grouped_supported(H, self.ff)):
                 # prompts: the grouped rows as one matrix, then both products on the tcgen05 tensor cores
                 xs = ws.get("moe_xs", (cap, H), x.dtype)
                 K.moe_gather(x, xs, sorted_pair, n_tiles, top, mt)
-                if self.gated:
+                if fused and n_up % 32 == 0:
+                    K.gemm_tc_grouped(xs, self.w_up, act, False, tile_expert, n_tiles, self.rt.status, gated_limit=self.limit)
+                elif self.gated:
+                    gu = ws.get("moe_gu", (cap, n_up), x.dtype)
                     K.gemm_tc_grouped(xs, self.w_up, gu, False, tile_expert, n_tiles, self.rt.status)
-                    K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit)
+                    K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit, tiled=self.tiled)
                 else:
                     K.gemm_tc_grouped(xs, self.w_up, act, True, tile_expert, n_tiles, self.rt.status)
                 K.gemm_tc_grouped(act, self.w_down, y, False, tile_expert, n_tiles, self.rt.status)
             else:
-                if self.gated:
+                if fused:
+                    K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt, gated_limit=self.limit)
+                elif self.gated:
                     K.moe_gemm(x, self.w_up, gu, False, sorted_pair, tile_expert, n_tiles, top, mt, plain=True)
                     K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit)
                 else:

@@ -16,7 +16,7 @@ from .base import KVRequest, LayerCache, Mixer, Runtime
 from .linear import matmul
 
 
-def decode_splits(ctx, n_q: int, n_kv: int, v_dim: int, dtype: torch.dtype, rt: Runtime):
+def decode_splits(ctx, n_q: int, n_kv: int, v_dim: int, dtype: torch.dtype, rt: Runtime, head_dim: int = 0):
     """(n_splits, split_len, scratch) of a step's attention: a step of single tokens cuts every sequence's keys into
     splits (float32: of a fixed length, so that where a sequence's partial sums are cut depends on its own length only;
     bfloat16: by the batch's size); any other step does not."""
@@ -26,7 +26,9 @@ def decode_splits(ctx, n_q: int, n_kv: int, v_dim: int, dtype: torch.dtype, rt: 
         split_len = FP32_SPLIT_LEN
         n_splits = max(1, -(-ctx.kv_len_bound // split_len))
     else:
-        n_splits, split_len = plan_splits(ctx.n_rows, n_kv, ctx.kv_len_bound, rt.sm_count)
+        # (the tensor-core kernel cuts a large group of query heads into several, each with CTAs of its own)
+        heads = K.attention_decode_heads(n_q, n_kv, head_dim, v_dim) if head_dim else n_kv
+        n_splits, split_len = plan_splits(ctx.n_rows, heads, ctx.kv_len_bound, rt.sm_count)
     scratch = None
     if n_splits > 1:
         scratch = ctx.ws.get("attn_scratch", (K.attention_scratch_floats(ctx.T, n_q, v_dim, n_splits),), torch.float32)
@@ -106,7 +108,7 @@ class QKNormedAttention(Mixer):
         K.norm_append(proj, q, self.q_norm, self.k_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool,
                       lc.v_pool, lc.group.table, self.n_kv, lc.writes, rt.status)
         attn = ws.get("nat_attn", (T, self.n_q * self.dv), x.dtype)
-        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, self.n_kv, self.dv, x.dtype, rt)
+        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, self.n_kv, self.dv, x.dtype, rt, self.d)
         K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
                     ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d, self.scale,
                     self.window or 0, n_splits, split_len, scratch, rt.status)
@@ -180,7 +182,7 @@ class LatentAttention(Mixer):
         qc = ws.get("lat_qc", (T, self.n_q * self.r), x.dtype)
         K.head_gemm(q, self.w_qc, qc)
         ac = ws.get("lat_ac", (T, self.n_q * self.r), x.dtype)
-        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, 1, self.r, x.dtype, rt)
+        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, 1, self.r, x.dtype, rt, self.r)
         K.attention(qc, lc.k_pool, lc.k_pool, ac, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
                     ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, 1, self.r, self.scale,
                     self.window or 0, n_splits, split_len, scratch, rt.status)

@@ -220,7 +220,11 @@ def test_window_edges_in_portions_and_token_by_token(dtype, case):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("r,G,window,bs,S", [(40, 3, None, 8, 300), (64, 4, None, 16, 700), (128, 2, None, 64, 400),
-                                             (96, 8, None, 64, 1100), (24, 5, 17, 8, 120)])
+                                             (96, 8, None, 64, 1100), (24, 5, 17, 8, 120),
+                                             # more query heads than the tensor-core decode kernel takes in one group:
+                                             # cut into groups of 8, of 5, and (a prime) left to the CUDA-core kernel
+                                             (64, 32, None, 16, 300), (128, 20, None, 64, 330), (64, 17, None, 8, 200),
+                                             (128, 40, 50, 16, 200)])
 def test_attention_over_cached_latents_far_keys(dtype, r, G, window, bs, S):
     """One pool read as keys and as values by all query heads; keys that stand out lie hundreds of positions back."""
     _window_case(dtype, r, r, G, 1, window, bs, S, [S], seed=4, shared=True)
