@@ -98,7 +98,10 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const int n_tiles = (hi - t_begin + PM_BN - 1) / PM_BN;
     issue(t_begin, 0);                                // this group also carries the queries
 
-    uint32_t qf[D / 16][4];
+    // head sizes above 128: the query fragments are read from shared memory for every key tile instead of being kept
+    // (with the output tile they would not fit the registers)
+    constexpr bool Q_REGS = D <= 128;
+    uint32_t qf[Q_REGS ? D / 16 : 1][4];
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -121,7 +124,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (it == 0) {
+        if (Q_REGS && it == 0) {
             const int mi = lane >> 3, r = warp * 16 + (mi & 1) * 8 + (lane & 7);
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks)
@@ -138,16 +141,21 @@ attn_prefill_mma_kernel(const AttnParams p) {
             for (int i = 0; i < PM_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
             {
                 const int mi = lane >> 3;
+                const int qr = warp * 16 + (mi & 1) * 8 + (lane & 7);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    uint32_t a0, a1, a2, a3;
+                    if (Q_REGS) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; }
+                    else ldmatrix_x4(smem_u32(q_s + swz<D>(qr, kk * 2 + (mi >> 1))), a0, a1, a2, a3);
 #pragma unroll
                     for (int np = 0; np < PM_BN / 16; ++np) {
                         const int r = np * 16 + (mi >> 1) * 8 + (lane & 7);
                         uint32_t b0, b1, b2, b3;
                         ldmatrix_x4(smem_u32(ks_ + swz<D>(r, kk * 2 + (mi & 1))), b0, b1, b2, b3);
-                        mma_bf16(s[np * 2], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
-                        mma_bf16(s[np * 2 + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+                        mma_bf16(s[np * 2], a0, a1, a2, a3, b0, b1);
+                        mma_bf16(s[np * 2 + 1], a0, a1, a2, a3, b2, b3);
                     }
+                }
             }
             const bool need_mask = t0 + PM_BN - 1 > w_first || t0 < lo || t0 + PM_BN > hi ||
                                    (p.window > 0 && t0 < w_last - p.window + 1) || t0 < cs_last;
@@ -252,6 +260,9 @@ int launch_attn_prefill_mma(const AttnParams& p, int n_rows, int max_q_len, cuda
     if (p.n_splits != 1) return 1;
     if (p.d == 128) return launch_pm<128>(p, n_rows, max_q_len, stream);
     if (p.d == 64) return launch_pm<64>(p, n_rows, max_q_len, stream);
+    // wider heads (one cached latent as key and value of many query heads): rows of whole 128-byte swizzle groups
+    if (p.d == 256) return launch_pm<256>(p, n_rows, max_q_len, stream);
+    if (p.d == 192) return launch_pm<192>(p, n_rows, max_q_len, stream);
     return 1;
 }
 

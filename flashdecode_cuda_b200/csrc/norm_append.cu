@@ -7,6 +7,8 @@
 //   q_out [T, nq]                      q / sqrt(mean(q^2) + eps) * q_w   (q_w null: q as it is)
 //   k_pool [blocks, n_kv, block_size, nk / n_kv]   the same with k_w
 //   v_pool [blocks, n_kv, block_size, nv / n_kv]   nv == 0: no values are kept (the keys serve as values)
+//   k_rows [T, nk] (optional)          the normed k once more as plain rows, for a product that follows
+// nq == 0: there is no q (the rows are keys and values only).
 //
 // With n_kv = 1 and nv = 0 the "key" is any normed vector per position, e.g. the
 // low-rank latent that a latent-attention mixer makes its keys and values from.
@@ -21,7 +23,7 @@ __global__ void norm_append_kernel(const T* __restrict__ proj, int ld, T* __rest
                                    const int* __restrict__ tok_row, const int* __restrict__ tok_pos,
                                    const int* __restrict__ row_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                    const int* __restrict__ block_table, int max_blocks, int num_blocks, int block_size,
-                                   int nq, int nk, int nv, int n_kv, int write_kv, int* status) {
+                                   int nq, int nk, int nv, int n_kv, int write_kv, T* __restrict__ k_rows, int* status) {
     __shared__ float red[40];
     const int t = blockIdx.x;
     const int slot = row_slot[tok_row[t]];
@@ -38,6 +40,13 @@ __global__ void norm_append_kernel(const T* __restrict__ proj, int ld, T* __rest
     for (int i = threadIdx.x; i < nq; i += blockDim.x) {
         const float v = to_float(row[i]);
         qo[i] = q_w != nullptr ? from_float<T>(v * rq * q_w[i]) : row[i];
+    }
+    if (k_rows != nullptr) {
+        T* kr = k_rows + (size_t)t * nk;
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+            const float v = to_float(row[nq + i]);
+            kr[i] = k_w != nullptr ? from_float<T>(v * rk * k_w[i]) : row[nq + i];
+        }
     }
     if (!write_kv) return;
     const int pos = tok_pos[t];
@@ -72,17 +81,20 @@ typedef __nv_bfloat16 bf16;
 extern "C" int fd_norm_append(const void* proj, int ld, void* q_out, int dtype, const float* q_w, const float* k_w,
                               float eps, const int* tok_row, const int* tok_pos, const int* row_slot, void* k_pool,
                               void* v_pool, const int* block_table, int max_blocks, int num_blocks, int block_size, int T,
-                              int nq, int nk, int nv, int n_kv, int write_kv, int* status, cudaStream_t stream) {
+                              int nq, int nk, int nv, int n_kv, int write_kv, void* k_rows, int* status,
+                              cudaStream_t stream) {
     if (T == 0) return 0;
-    FD_REQUIRE(nq > 0 && nk > 0 && nv >= 0 && n_kv > 0 && nk % n_kv == 0 && nv % n_kv == 0 && ld >= nq + nk + nv, -2,
+    FD_REQUIRE(nq >= 0 && (nq == 0 || q_out != nullptr) && nk > 0 && nv >= 0 && n_kv > 0 && nk % n_kv == 0 && nv % n_kv == 0 && ld >= nq + nk + nv, -2,
                "norm_append: %d + %d + %d columns of %d for %d key heads", nq, nk, nv, ld, n_kv);
     FD_REQUIRE(block_size > 0 && (nv == 0 || v_pool != nullptr), -2, "norm_append: bad cache arguments");
     const int threads = nq + nk >= 1024 ? 256 : 128;
     if (dtype == 0)
         return launch("norm_append", norm_append_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
                       (const float*)proj, ld, (float*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (float*)k_pool,
-                      (float*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv, status);
+                      (float*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv,
+                      (float*)k_rows, status);
     return launch("norm_append", norm_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
                   (const bf16*)proj, ld, (bf16*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (bf16*)k_pool,
-                  (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv, status);
+                  (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv,
+                  (bf16*)k_rows, status);
 }

@@ -131,7 +131,11 @@ class LatentAttention(Mixer):
     into the latent's basis (one small product per head), attention runs over the cached latents as ONE key/value head
     of size ``kv_rank`` that all query heads share and that serves as key and as value, and V_h is applied to each
     head's attended latent afterwards.  Visible keys: j <= i, and with a ``window`` only i - j < window.
-    Tensors ``<prefix>.q``, ``.dkv``, ``.dkv.norm``, ``.uk``, ``.uv``, ``.o``.
+
+    Whole prompts in bfloat16 (a step whose sequences all start at their first token) take the other order where that
+    reaches a faster attention kernel: k_h and v_h of the step's own tokens are expanded by one product into pages of the
+    workspace, and attention runs over them with a key/value head per query head (``expands``); the cache still
+    receives the latents only.  Tensors ``<prefix>.q``, ``.dkv``, ``.dkv.norm``, ``.uk``, ``.uv``, ``.o``.
     """
 
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int, kv_rank: int,
@@ -162,11 +166,19 @@ class LatentAttention(Mixer):
         self.w_in = torch.cat([tensors.pop(f"{p}.q"), tensors.pop(f"{p}.dkv")], dim=0).contiguous()     # [q | latent]
         self.c_norm = tensors[f"{p}.dkv.norm"].float().contiguous()
         # per head: U_h^T [kv_rank, head_dim] takes a query into the latent's basis; V_h [v_head_dim, kv_rank]
-        self.w_qc = tensors.pop(f"{p}.uk").view(self.n_q, self.d, self.r).transpose(1, 2).contiguous()
-        self.w_cv = tensors.pop(f"{p}.uv").view(self.n_q, self.dv, self.r).contiguous()
+        uk, uv = tensors.pop(f"{p}.uk"), tensors.pop(f"{p}.uv")
+        self.w_qc = uk.view(self.n_q, self.d, self.r).transpose(1, 2).contiguous()
+        self.w_cv = uv.view(self.n_q, self.dv, self.r).contiguous()
         self.w_o = tensors[f"{p}.o"]
+        # which attention kernel each order reaches (3 tcgen05, 2 mma.sync, 1 mma.sync at wide heads, 0 CUDA cores)
+        rank = lambda size: {128: 3, 64: 2, 192: 1, 256: 1}.get(size, 0)
+        latent, expanded = rank(self.r), (rank(self.d) if self.d == self.dv else 0)
+        self.expands = rt.dtype == torch.bfloat16 and (expanded > latent or (expanded == latent and expanded > 1
+                                                                              and 2 * self.r > self.d + self.dv))
+        self.w_kv = torch.cat([uk, uv], dim=0).contiguous() if self.expands else None      # [heads (d + dv), kv_rank]
 
     def weight_bytes(self) -> int:
+        # (the expansion matrix is a second copy of .uk and .uv in another order: a step reads one of the two)
         return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_qc, self.w_cv, self.w_o))
 
     def first_weights(self) -> Optional[torch.Tensor]:
@@ -177,6 +189,30 @@ class LatentAttention(Mixer):
         proj = ws.get("lat_proj", (T, self.w_in.shape[0]), x.dtype)
         matmul(x, self.w_in, None, proj, status=rt.status)
         q = ws.get("lat_q", (T, self.n_q * self.d), x.dtype)
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        if self.expands and ctx.max_q_len > 1 and not any(ctx.h_ctx_len):
+            # whole prompts: expand the step's own keys and values and attend over them
+            c = ws.get("lat_c", (T, self.r), x.dtype)
+            K.norm_append(proj, q, None, self.c_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, None,
+                          lc.group.table, 1, lc.writes, rt.status, k_rows=c)
+            kv = ws.get("lat_kv", (T, self.w_kv.shape[0]), x.dtype)
+            matmul(c, self.w_kv, None, kv, status=rt.status)
+            bs = lc.group.block_size
+            per_row = -(-ctx.max_q_len // bs)
+            n_blocks = ctx.n_rows * per_row
+            k_tmp = ws.get("lat_k_pages", (n_blocks, self.n_q, bs, self.d), x.dtype)
+            v_tmp = ws.get("lat_v_pages", (n_blocks, self.n_q, bs, self.dv), x.dtype)
+            table = ws.get("lat_page_table", (ctx.n_rows, per_row), torch.int32)       # row i owns pages i * per_row ...
+            torch.arange(n_blocks, out=table.view(-1))
+            rows = ws.get("lat_page_rows", (ctx.n_rows,), torch.int32)
+            torch.arange(ctx.n_rows, out=rows)
+            K.norm_append(kv, None, None, None, self.eps, ctx.tok_row, ctx.tok_pos, rows, k_tmp, v_tmp, table, self.n_q,
+                          True, rt.status)
+            av = ws.get("lat_v", (T, self.n_q * self.dv), x.dtype)
+            K.attention(q, k_tmp, v_tmp, av, table, ctx.tok_row, rows, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len,
+                        ctx.n_rows, ctx.max_q_len, self.n_q, self.n_q, self.d, self.scale, self.window or 0, 1, 0, None,
+                        rt.status)
+            return matmul(av, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)
         K.norm_append(proj, q, None, self.c_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, None,
                       lc.group.table, 1, lc.writes, rt.status)
         qc = ws.get("lat_qc", (T, self.n_q * self.r), x.dtype)
@@ -188,5 +224,4 @@ class LatentAttention(Mixer):
                     self.window or 0, n_splits, split_len, scratch, rt.status)
         v = ws.get("lat_v", (T, self.n_q * self.dv), x.dtype)
         K.head_gemm(ac, self.w_cv, v)
-        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
         return matmul(v, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)

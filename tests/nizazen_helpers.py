@@ -61,6 +61,11 @@ NIZAZEN: Dict[str, dict] = {
           "layers": [_layer(_att(2, 1, 16, 24, 0.3, 1), _moe(3, 3, 16, 2.0)),
                      _layer(_lat(5, 8, 16, 24, 0.35, 17), _dense(40)),
                      _layer(_att(6, 3, 8, 8, 0.35, 9), _moe(7, 3, 24, 1.0))]},
+    # latent layers whose whole prompts attend over expanded keys and values (head sizes 64 and 128 for keys and values
+    # alike, latents of other sizes), one of them with a window; two lanes
+    "S": {"architecture": "Nizazen", "vocab": 120, "width": 64, "norm": {"eps": 1e-5}, "streams": 2, "logit_softcap": 20.0,
+          "layers": [_layer(_lat(2, 64, 64, 24, 0.125), _dense(48)),
+                     _layer(_lat(3, 128, 128, 192, 0.09, 50), _moe(3, 2, 16, 1.0))]},
 }
 
 
@@ -76,7 +81,8 @@ def random_config(seed: int) -> dict:
             kv, g = rng.choice([1, 2, 3]), rng.choice([1, 2, 4])
             dim = rng.choice([8, 16, 24, 40, 64, 128])
             return _att(kv * g, kv, dim, rng.choice([dim, 8, 16, 48, 80]), rng.choice([0.1, 0.125, 0.3]), window)
-        return _lat(rng.choice([1, 2, 5, 8]), rng.choice([4, 8, 20, 32]), rng.choice([4, 8, 24, 40]),
+        dim = rng.choice([4, 8, 20, 32, 64])
+        return _lat(rng.choice([1, 2, 5, 8]), dim, rng.choice([dim, 4, 8, 24, 40]),
                     rng.choice([8, 24, 64, 96, 128]), rng.choice([0.1, 0.2, 0.3]), rng.choice([None, None, window]))
 
     def mlp():

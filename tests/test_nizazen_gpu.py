@@ -25,7 +25,7 @@ from plain import nizazen_plain as P
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 DEV = "cuda"
-NAMES = ["P", "Q", "R"]
+NAMES = ["P", "Q", "R", "S"]
 DTYPES = ["float32", "bfloat16"]
 TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 KTOL = {"float32": 2e-5, "bfloat16": 2e-2}
@@ -224,7 +224,9 @@ def test_window_edges_in_portions_and_token_by_token(dtype, case):
                                              # more query heads than the tensor-core decode kernel takes in one group:
                                              # cut into groups of 8, of 5, and (a prime) left to the CUDA-core kernel
                                              (64, 32, None, 16, 300), (128, 20, None, 64, 330), (64, 17, None, 8, 200),
-                                             (128, 40, 50, 16, 200)])
+                                             (128, 40, 50, 16, 200),
+                                             # latents wider than 128: prompts on the mma.sync kernel's wide forms
+                                             (256, 8, None, 64, 500), (192, 3, 40, 16, 300)])
 def test_attention_over_cached_latents_far_keys(dtype, r, G, window, bs, S):
     """One pool read as keys and as values by all query heads; keys that stand out lie hundreds of positions back."""
     _window_case(dtype, r, r, G, 1, window, bs, S, [S], seed=4, shared=True)
@@ -318,7 +320,8 @@ def _vocab(name):
 
 
 def _lengths(name):
-    return {"P": [1, 2, 19, 20, 21, 75, 140], "Q": [3, 64, 65, 260], "R": [1, 9, 10, 17, 18, 129]}[name]
+    return {"P": [1, 2, 19, 20, 21, 75, 140], "Q": [3, 64, 65, 260], "R": [1, 9, 10, 17, 18, 129],
+            "S": [1, 2, 50, 51, 130, 200]}[name]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -359,7 +362,7 @@ def test_prefill_then_token_by_token_across_window_edges(engines, folders, name,
     """A prompt, then so many single tokens that every window of the model passes over decoded tokens only."""
     eng = engines[(name, dtype)]
     cache = eng.model.new_cache(max_tokens=256, block_size=16)
-    n_decode = {"P": 150, "Q": 80, "R": 40}[name]
+    n_decode = {"P": 150, "Q": 80, "R": 40, "S": 70}[name]
     for head in (1, 30):
         (p,) = prompts_for(_vocab(name), [head + n_decode], seed=3 + head)
         want = oracle_logits(folders[(name, dtype)], p)
@@ -489,7 +492,7 @@ def test_greedy_generation_through_the_engine(folders, name):
     eng.model.check_status()
 
 
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "S"])
 def test_greedy_generation_in_bfloat16_picks_a_best_token(folders, name):
     folder = folders[(name, "bfloat16")]
     eng = fd.load(folder, device="cuda", dtype="bfloat16")
