@@ -1,6 +1,6 @@
 """flashdecode_cuda_b200: a small generation library for the Qwen2 dense
-decoder and the Lonasun decoder on one NVIDIA B200 (sm_100a), with hand-written
-CUDA kernels.
+decoder, the Lonasun decoder and the Nizazen decoder on one NVIDIA B200
+(sm_100a), with hand-written CUDA kernels.
 
     import flashdecode_cuda_b200 as fd
     engine = fd.load("/path/to/model_folder", device="cuda", dtype="bfloat16")
