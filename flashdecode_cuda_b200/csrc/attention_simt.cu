@@ -32,6 +32,12 @@ constexpr int RPW = RMAX / ATT_WARPS;   // rows per warp in the score phase
 constexpr int RPT_MAX = 16;     // rows per thread in the value phase
 
 
+// Heads wider than 256 (one cached latent as key and value of many query heads): a CTA takes at most RWIDE query rows,
+// which is what its threads' value accumulators and its shared memory hold at those widths.
+constexpr int RWIDE = 32;
+constexpr int D_MAX = 512;
+__host__ __device__ __forceinline__ int q_rows_alloc(int d, int dv) { return d > 256 || dv > 256 ? RWIDE : RMAX; }
+
 template <typename T> struct Pad;            // padding of a key row in shared memory, in elements
 template <> struct Pad<float> { static constexpr int v = 4; };
 template <> struct Pad<__nv_bfloat16> { static constexpr int v = 4; };
@@ -78,8 +84,8 @@ attn_tile_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int KPAD = Pad<T>::v;
     const int kstride = d + KPAD;
-    float* q_s = reinterpret_cast<float*>(smem_raw);               // [RMAX][d]
-    float* p_s = q_s + RMAX * d;                                      // [RMAX][KT]
+    float* q_s = reinterpret_cast<float*>(smem_raw);               // [RMAX][d] ([RWIDE][d] for heads wider than 256)
+    float* p_s = q_s + q_rows_alloc(d, dv) * d;                       // [RMAX][KT]
     float* alpha_s = p_s + RMAX * KT;                                 // [RMAX]
     float* l_s = alpha_s + RMAX;                                      // [RMAX]
     T* v_s = reinterpret_cast<T*>(l_s + RMAX);                        // [KT][dv]
@@ -312,7 +318,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
 
 template <typename T>
 static size_t attn_smem_bytes(int d, int dv) {
-    return (size_t)(RMAX * d + RMAX * KT + 2 * RMAX) * sizeof(float) +
+    return (size_t)(q_rows_alloc(d, dv) * d + RMAX * KT + 2 * RMAX) * sizeof(float) +
            (size_t)(KT * dv + KT * (d + Pad<T>::v)) * sizeof(T);
 }
 
@@ -371,8 +377,9 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
-    FD_REQUIRE(d % 8 == 0 && d >= 8 && d <= 256, -2, "attention: head size %d must be a multiple of 8 in [8, 256]", d);
-    FD_REQUIRE(dv % 8 == 0 && dv >= 8 && dv <= 256, -2, "attention: value head size %d must be a multiple of 8 in [8, 256]", dv);
+    FD_REQUIRE(d % 8 == 0 && d >= 8 && d <= D_MAX, -2, "attention: head size %d must be a multiple of 8 in [8, %d]", d, D_MAX);
+    FD_REQUIRE(dv % 8 == 0 && dv >= 8 && dv <= D_MAX, -2, "attention: value head size %d must be a multiple of 8 in [8, %d]", dv, D_MAX);
+    FD_REQUIRE((d <= 256 && dv <= 256) || G <= RWIDE, -2, "attention: heads wider than 256 take groups of up to %d query heads, got %d", RWIDE, G);
     FD_REQUIRE(chunk >= 0 && window >= 0, -2, "attention: chunk %d and window %d must not be negative", chunk, window);
     FD_REQUIRE(G <= RMAX, -2, "attention: group size %d exceeds %d", G, RMAX);
     FD_REQUIRE(block_size > 0, -2, "attention: block size %d", block_size);
@@ -402,6 +409,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.n_kv_pool = n_kv; p.kv_div = 1;
     if (dv != d) use_mma = 0;          // the tensor-core kernels keep keys and values of one size
     int qt = fd_attn_simt_qt(G);
+    if ((d > 256 || dv > 256) && qt > RWIDE / G) qt = RWIDE / G;
     if (qt > max_q_len) qt = max_q_len;
     p.QT = qt; p.n_splits = n_splits; p.split_len = split_len; p.window = window; p.scale = scale;
 

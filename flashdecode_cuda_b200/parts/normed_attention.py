@@ -37,9 +37,9 @@ def decode_splits(ctx, n_q: int, n_kv: int, v_dim: int, dtype: torch.dtype, rt: 
 
 def _head_sizes_ok(prefix: str, **sizes: int) -> None:
     for what, n in sizes.items():
-        if n < 8 or n > 256 or n % 8 != 0:
+        if n < 8 or n > 512 or n % 8 != 0:
             raise ValueError(f"{prefix}: {what.replace('_', ' ')} {n} is not taken: the attention kernels take multiples "
-                             f"of 8 from 8 to 256")
+                             f"of 8 from 8 to 512")
 
 
 @register_part("mixer", "qk_normed_attention")
@@ -141,9 +141,9 @@ class LatentAttention(Mixer):
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int, kv_rank: int,
                  scale: float, eps: float, window: Optional[int] = None):
         _head_sizes_ok(prefix, latent_size=kv_rank)
-        if n_heads < 1 or n_heads > 64 or head_dim < 1 or v_head_dim < 1:
+        if n_heads < 1 or n_heads > (64 if kv_rank <= 256 else 32) or head_dim < 1 or v_head_dim < 1:
             raise ValueError(f"{prefix}: {n_heads} heads of {head_dim} / {v_head_dim}: the attention kernel takes up to 64 "
-                             f"query heads on the one latent")
+                             f"query heads on the one latent (32 on a latent wider than 256)")
         self.prefix, self.hidden_size = prefix, hidden_size
         self.n_q, self.d, self.dv, self.r = n_heads, head_dim, v_head_dim, kv_rank
         self.scale, self.eps, self.window = float(scale), float(eps), window

@@ -226,7 +226,9 @@ def test_window_edges_in_portions_and_token_by_token(dtype, case):
                                              (64, 32, None, 16, 300), (128, 20, None, 64, 330), (64, 17, None, 8, 200),
                                              (128, 40, 50, 16, 200),
                                              # latents wider than 128: prompts on the mma.sync kernel's wide forms
-                                             (256, 8, None, 64, 500), (192, 3, 40, 16, 300)])
+                                             (256, 8, None, 64, 500), (192, 3, 40, 16, 300),
+                                             # wider than any tensor-core kernel takes: the CUDA-core kernel's narrow tiles
+                                             (384, 4, None, 16, 200), (512, 8, 70, 64, 260), (320, 32, None, 8, 90)])
 def test_attention_over_cached_latents_far_keys(dtype, r, G, window, bs, S):
     """One pool read as keys and as values by all query heads; keys that stand out lie hundreds of positions back."""
     _window_case(dtype, r, r, G, 1, window, bs, S, [S], seed=4, shared=True)
