@@ -49,9 +49,11 @@ template <> __device__ __forceinline__ void store_vec<__nv_bfloat16>(__nv_bfloat
     } else p[0] = __float2bfloat16_rn(v[0]);
 }
 
+// LM: the most lanes this instantiation holds in registers (2, 4 or 8: with 8 the kernel needs 121 registers and two CTAs
+// fit an SM; most models have 2 to 4 lanes).
 // VEC = 4: a thread takes four neighbouring channels of every lane (16-byte loads and stores; H a multiple of 4 and
 // all pointers 16-byte aligned); VEC = 1: any width.  The arithmetic per channel is the same in both.
-template <typename TD, typename TO, int VEC>
+template <typename TD, typename TO, int VEC, int LM>
 __global__ void lanes_norm_kernel(const TD* __restrict__ y, int n_parts, size_t part_stride,
                                   const float* __restrict__ gain, const float* __restrict__ mix,
                                   const float* __restrict__ back, float* __restrict__ lanes, int write_lanes,
@@ -77,9 +79,9 @@ __global__ void lanes_norm_kernel(const TD* __restrict__ y, int n_parts, size_t 
     float* base = lanes + (size_t)r * S * H;
     float ss = 0.f;
     for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
-        float x[LANES_MAX][VEC];
+        float x[LM][VEC];
 #pragma unroll
-        for (int s = 0; s < LANES_MAX; ++s) {
+        for (int s = 0; s < LM; ++s) {
             if (s < S) load_vec<float>(base + (size_t)s * H + i, x[s], VEC);
             else {
 #pragma unroll
@@ -105,13 +107,13 @@ __global__ void lanes_norm_kernel(const TD* __restrict__ y, int n_parts, size_t 
                 for (int e = 0; e < VEC; ++e) z[e] *= g[e];
             }
 #pragma unroll
-            for (int t = 0; t < LANES_MAX; ++t) {
+            for (int t = 0; t < LM; ++t) {
                 if (t < S) {
                     float n[VEC];
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) n[e] = 0.f;
 #pragma unroll
-                    for (int s = 0; s < LANES_MAX; ++s)
+                    for (int s = 0; s < LM; ++s)
                         if (s < S) {
                             const float m = m_s[s * S + t];
 #pragma unroll
@@ -128,7 +130,7 @@ __global__ void lanes_norm_kernel(const TD* __restrict__ y, int n_parts, size_t 
             }
         } else {
 #pragma unroll
-            for (int t = 0; t < LANES_MAX; ++t)
+            for (int t = 0; t < LM; ++t)
                 if (t < S) {
                     const float at = a_s[t];
 #pragma unroll
@@ -207,7 +209,8 @@ extern "C" int fd_lanes_norm(const void* y, int y_dtype, int n_parts, long long 
     const int threads = vec ? (H >= 2048 ? 256 : 128) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
 #define FD_LN1(TD_, TO_, V_)                                                                                         \
     do {                                                                                                             \
-        auto k = lanes_norm_kernel<TD_, TO_, V_>;                                                                    \
+        auto k = S <= 2 ? lanes_norm_kernel<TD_, TO_, V_, 2> : (S <= 4 ? lanes_norm_kernel<TD_, TO_, V_, 4>             \
+                                                                       : lanes_norm_kernel<TD_, TO_, V_, 8>);           \
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
         return launch("lanes_norm", k, dim3(n_out), dim3(threads), smem, stream, dim3(1, 1, 1), (const TD_*)y, n_parts, \
                       (size_t)part_stride, gain, mix, back, lanes, write_lanes, read, w, eps, (TO_*)out, rows, H, S); \
