@@ -91,6 +91,7 @@ attn_tile_kernel(const AttnParams p) {
     T* v_s = reinterpret_cast<T*>(l_s + RMAX);                        // [KT][dv]
     T* k_s = v_s + KT * dv;                                           // [KT][d + KPAD]
 
+    __shared__ int row_s[KT];                    // per token of the tile: its row in the pools, -1 outside [lo, hi)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const T* qg = static_cast<const T*>(p.q);
     const T* kp = static_cast<const T*>(p.k_pool);
@@ -124,28 +125,51 @@ attn_tile_kernel(const AttnParams p) {
 
     for (int t0 = (lo / KT) * KT; t0 < hi; t0 += KT) {
         __syncthreads();   // previous tile consumed (and q_s written, first time round)
-        // stage keys and values of this tile; tokens outside [lo, hi) read as zero
-        for (int c = tid; c < KT * (cpr + cprv); c += ATT_THREADS) {
-            const int tt = c / (cpr + cprv), cc = c - tt * (cpr + cprv);
-            const bool is_v = cc >= cpr;
-            const int t = t0 + tt;
-            uint4 x4 = make_uint4(0, 0, 0, 0);
+        // stage keys and values of this tile; tokens outside [lo, hi) read as zero.  The tile's block numbers are looked
+        // up once per token, then every thread has several independent 16-byte loads in flight (one lookup and one
+        // load at a time, each waiting for the one before, made a decode step at wide heads four times as long)
+        if (tid < KT) {
+            const int t = t0 + tid;
+            int base = -1;
             if (t >= lo && t < hi) {
                 const int blk = p.block_table[(size_t)slot * p.max_blocks + t / bs];
-                if (blk < 0 || blk >= p.num_blocks) {
-                    set_status(p.status, STATUS_BAD_BLOCK);
-                } else if (is_v) {
-                    x4 = *reinterpret_cast<const uint4*>(vp + (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * dv + (cc - cpr) * EPC);
-                } else {
-                    x4 = *reinterpret_cast<const uint4*>(kp + (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * d + cc * EPC);
-                }
+                if (blk < 0 || blk >= p.num_blocks) set_status(p.status, STATUS_BAD_BLOCK);
+                else base = (blk * p.n_kv + kvh) * bs + (t % bs);          // the token's row in either pool
             }
-            if (is_v) {
-                *reinterpret_cast<uint4*>(v_s + tt * dv + (cc - cpr) * EPC) = x4;
-            } else {
-                uint2* kd = reinterpret_cast<uint2*>(k_s + tt * kstride + cc * EPC);
-                kd[0] = make_uint2(x4.x, x4.y);
-                kd[1] = make_uint2(x4.z, x4.w);
+            row_s[tid] = base;
+        }
+        __syncthreads();
+        {
+            constexpr int UNR = 4;
+            const int per_tok = cpr + cprv, total = KT * per_tok;
+            for (int c0 = tid; c0 < total; c0 += ATT_THREADS * UNR) {
+                uint4 x4[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int c = c0 + u * ATT_THREADS;
+                    x4[u] = make_uint4(0, 0, 0, 0);
+                    if (c < total) {
+                        const int tt = c / per_tok, cc = c - tt * per_tok;
+                        const int base = row_s[tt];
+                        if (base >= 0)
+                            x4[u] = cc >= cpr ? *reinterpret_cast<const uint4*>(vp + (size_t)base * dv + (cc - cpr) * EPC)
+                                              : *reinterpret_cast<const uint4*>(kp + (size_t)base * d + cc * EPC);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int c = c0 + u * ATT_THREADS;
+                    if (c < total) {
+                        const int tt = c / per_tok, cc = c - tt * per_tok;
+                        if (cc >= cpr) {
+                            *reinterpret_cast<uint4*>(v_s + tt * dv + (cc - cpr) * EPC) = x4[u];
+                        } else {
+                            uint2* kd = reinterpret_cast<uint2*>(k_s + tt * kstride + cc * EPC);
+                            kd[0] = make_uint2(x4[u].x, x4[u].y);
+                            kd[1] = make_uint2(x4[u].z, x4[u].w);
+                        }
+                    }
+                }
             }
         }
         __syncthreads();
@@ -161,13 +185,13 @@ attn_tile_kernel(const AttnParams p) {
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
                 const int r = warp + i * ATT_WARPS;
-                if (r < R) {
-                    const float4 qv = *reinterpret_cast<const float4*>(q_s + r * d + c * 4);
-                    s[i] = fmaf(qv.x, kf[0], s[i]);
-                    s[i] = fmaf(qv.y, kf[1], s[i]);
-                    s[i] = fmaf(qv.z, kf[2], s[i]);
-                    s[i] = fmaf(qv.w, kf[3], s[i]);
-                }
+                if (r >= R) break;          // rows grow with i: nothing of a decode step's few rows is left (the unrolled
+                                            // loops' skipped iterations were most of this kernel's instructions there)
+                const float4 qv = *reinterpret_cast<const float4*>(q_s + r * d + c * 4);
+                s[i] = fmaf(qv.x, kf[0], s[i]);
+                s[i] = fmaf(qv.y, kf[1], s[i]);
+                s[i] = fmaf(qv.z, kf[2], s[i]);
+                s[i] = fmaf(qv.w, kf[3], s[i]);
             }
         }
         // online softmax, one row per warp at a time
@@ -175,7 +199,8 @@ attn_tile_kernel(const AttnParams p) {
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
             const int r = warp + i * ATT_WARPS;
-            if (r < R) {
+            if (r >= R) break;
+            {
                 const int qpos = p_first + r / G;
                 const bool valid = t >= lo && t < hi && t <= qpos && (p.window <= 0 || qpos - t < p.window) &&
                                    (p.chunk <= 0 || t >= (qpos / p.chunk) * p.chunk);
@@ -199,10 +224,9 @@ attn_tile_kernel(const AttnParams p) {
 #pragma unroll
             for (int i = 0; i < RPT_MAX; ++i) {
                 const int r = rg + i * RG;
-                if (r < R) {
-                    const float a = alpha_s[r];
-                    acc[i][0] *= a; acc[i][1] *= a; acc[i][2] *= a; acc[i][3] *= a;
-                }
+                if (r >= R) break;
+                const float a = alpha_s[r];
+                acc[i][0] *= a; acc[i][1] *= a; acc[i][2] *= a; acc[i][3] *= a;
             }
             for (int tt = 0; tt < KT; ++tt) {
                 float vf[4];
@@ -210,13 +234,12 @@ attn_tile_kernel(const AttnParams p) {
 #pragma unroll
                 for (int i = 0; i < RPT_MAX; ++i) {
                     const int r = rg + i * RG;
-                    if (r < R) {
-                        const float pr = p_s[r * KT + tt];
-                        acc[i][0] = fmaf(pr, vf[0], acc[i][0]);
-                        acc[i][1] = fmaf(pr, vf[1], acc[i][1]);
-                        acc[i][2] = fmaf(pr, vf[2], acc[i][2]);
-                        acc[i][3] = fmaf(pr, vf[3], acc[i][3]);
-                    }
+                    if (r >= R) break;
+                    const float pr = p_s[r * KT + tt];
+                    acc[i][0] = fmaf(pr, vf[0], acc[i][0]);
+                    acc[i][1] = fmaf(pr, vf[1], acc[i][1]);
+                    acc[i][2] = fmaf(pr, vf[2], acc[i][2]);
+                    acc[i][3] = fmaf(pr, vf[3], acc[i][3]);
                 }
             }
         }
