@@ -83,7 +83,7 @@ def random_config(seed: int) -> dict:
             return _att(kv * g, kv, dim, rng.choice([dim, 8, 16, 48, 80]), rng.choice([0.1, 0.125, 0.3]), window)
         dim = rng.choice([4, 8, 20, 32, 64])
         return _lat(rng.choice([1, 2, 5, 8]), dim, rng.choice([dim, 4, 8, 24, 40]),
-                    rng.choice([8, 24, 64, 96, 128]), rng.choice([0.1, 0.2, 0.3]), rng.choice([None, None, window]))
+                    rng.choice([8, 24, 64, 104, 128]), rng.choice([0.1, 0.2, 0.3]), rng.choice([None, None, window]))
 
     def mlp():
         r = rng.random()
@@ -98,7 +98,7 @@ def random_config(seed: int) -> dict:
     if rng.random() < 0.8:
         cfg["streams"] = rng.choice([1, 2, 3, 4, 5])
     if rng.random() < 0.7:
-        cfg["logit_softcap"] = rng.choice([3.0, 15.0, 50.0])
+        cfg["logit_softcap"] = rng.choice([3.0, 12.0, 50.0])
     return cfg
 
 

@@ -220,7 +220,7 @@ def test_window_edges_in_portions_and_token_by_token(dtype, case):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("r,G,window,bs,S", [(40, 3, None, 8, 300), (64, 4, None, 16, 700), (128, 2, None, 64, 400),
-                                             (96, 8, None, 64, 1100), (24, 5, 17, 8, 120),
+                                             (88, 7, None, 64, 1100), (24, 5, 17, 8, 120),
                                              # more query heads than the tensor-core decode kernel takes in one group:
                                              # cut into groups of 8, of 5, and (a prime) left to the CUDA-core kernel
                                              (64, 32, None, 16, 300), (128, 20, None, 64, 330), (64, 17, None, 8, 200),
@@ -295,8 +295,8 @@ def test_gated_feed_forward_with_biases(dtype, H, I, T):
 
 def test_soft_cap():
     x = torch.randn(7, 333, device=DEV) * 40
-    want = 15.0 * torch.tanh(x.double() / 15.0)
-    K.softcap(x, 15.0)
+    want = 11.0 * torch.tanh(x.double() / 11.0)
+    K.softcap(x, 11.0)
     assert rel_err(x, want) < 1e-6
 
 
