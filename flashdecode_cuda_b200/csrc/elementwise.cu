@@ -8,23 +8,26 @@
 namespace fd {
 
 // ---------------------------------------------------------------------------
-// embedding: resid[t, :] = float(table[token[t], :])
+// embedding: resid[t, c, :] = float(table[token[t], :]) for each of the `copies` lanes c of the residual stream
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ resid, int H, int V, int* status) {
+                             float* __restrict__ resid, int H, int V, int copies, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t];
-    float* dst = resid + (size_t)t * H;
+    float* dst = resid + (size_t)t * copies * H;
     if (id < 0 || id >= V) {
         if (threadIdx.x == 0) set_status(status, STATUS_BAD_TOKEN);
-        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = 0.f;
+        for (int i = threadIdx.x; i < copies * H; i += blockDim.x) dst[i] = 0.f;
         return;
     }
     const TW* src = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(src[i]);
+        for (int c = 0; c < copies; ++c) dst[(size_t)c * H + i] = v;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -331,15 +334,15 @@ using namespace fd;
 typedef __nv_bfloat16 bf16;
 
 extern "C" int fd_embed(const int* tokens, const void* table, int table_dtype, float* resid,
-                        int T, int H, int V, int* status, cudaStream_t stream) {
+                        int T, int H, int V, int copies, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
-    FD_REQUIRE(H > 0 && V > 0, -2, "embed: bad sizes H=%d V=%d", H, V);
+    FD_REQUIRE(H > 0 && V > 0 && copies >= 1, -2, "embed: bad sizes H=%d V=%d copies=%d", H, V, copies);
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == 0)
         return launch("embed", embed_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), tokens,
-                      (const float*)table, resid, H, V, status);
+                      (const float*)table, resid, H, V, copies, status);
     return launch("embed", embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), tokens,
-                  (const bf16*)table, resid, H, V, status);
+                  (const bf16*)table, resid, H, V, copies, status);
 }
 
 template <typename TD, typename TO>

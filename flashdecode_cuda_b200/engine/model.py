@@ -385,17 +385,11 @@ class Model:
         (float32, a view of workspace memory that the next step overwrites)."""
         lanes = self.blueprint.lanes
         resid = ctx.ws.get("resid", (ctx.T, lanes * self.hidden_size), torch.float32)
-        embedded = None
-        if lanes > 1:
-            # a stream of several lanes: every lane starts as the embedding output
-            embedded = ctx.ws.get("embedded", (ctx.T, self.hidden_size), torch.float32)
-            self.embedding.forward(ctx, embedded)
-            K.lanes_fill(embedded, resid, lanes)
-        else:
-            self.embedding.forward(ctx, resid)
+        self.embedding.forward(ctx, resid)           # a stream of several lanes: every lane starts as the embedding output
         if self.trace is not None:
-            self.trace["embed"] = (resid if embedded is None else embedded).detach().float().cpu().clone()
-        if self.stream_ops and embedded is None:
+            self.trace["embed"] = resid[:, :self.hidden_size].detach().float().cpu().clone()
+        embedded = None
+        if self.stream_ops:
             # stream operations may read the embedding output again later in the step
             embedded = ctx.ws.get("embedded", (ctx.T, self.hidden_size), torch.float32)
             embedded.copy_(resid)

@@ -70,7 +70,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_device_arch": [],
         "fd_set_pdl": [I],
         "fd_sm_count": [],
-        "fd_embed": [P, P, I, P, I, I, I, P, P],
+        "fd_embed": [P, P, I, P, I, I, I, I, P, P],
         "fd_add_rmsnorm": [P, I, I, LL, P, I, P, I, F, P, I, P, I, I, P],
         "fd_silu_mul": [P, P, I, I, I, I, P],
         "fd_rope_append": [P, I, I, LL, P, I, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
@@ -209,11 +209,12 @@ def status_message(word: int) -> str:
 # ---------------------------------------------------------------------------
 
 def embed(tokens: torch.Tensor, table: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
-    """resid[t] = float(table[tokens[t]]); tokens int32 [T], resid float32 [T, H]."""
+    """resid[t] = float(table[tokens[t]]); tokens int32 [T], resid float32 [T, H] - or [T, lanes * H], a residual
+    stream of several lanes, every one of which receives the row."""
     T = tokens.numel()
     V, H = table.shape
-    assert tokens.dtype == torch.int32 and resid.dtype == torch.float32 and resid.shape[-1] == H
-    _check(lib().fd_embed(_ptr(tokens), _ptr(table), _dt(table.dtype), _ptr(resid), T, H, V,
+    assert tokens.dtype == torch.int32 and resid.dtype == torch.float32 and resid.shape[-1] % H == 0
+    _check(lib().fd_embed(_ptr(tokens), _ptr(table), _dt(table.dtype), _ptr(resid), T, H, V, resid.shape[-1] // H,
                           _ptr(status), _stream()))
 
 

@@ -15,7 +15,8 @@ from .base import Embedding, Runtime
 @register_part("embedding", "token_table")
 class TokenEmbedding(Embedding):
     """resid[t] = table[token[t]], unscaled (engine/model.py:166,255 of
-    davidjoyme/flashdecode-cuda), written as float32."""
+    davidjoyme/flashdecode-cuda), written as float32; into every lane of a
+    residual stream that has several ([T, lanes * hidden_size])."""
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tensor: Optional[str] = None):
         self.name = tensor or f"{prefix}.weight"        # ``tensor``: the table's full name where it is not <prefix>.weight

@@ -15,6 +15,10 @@ from .linear import fused_prompt_gemm, matmul
 # Up to this many tokens the routing kernel makes the router's logits itself (one launch, a CTA per token, each reading
 # the whole router matrix); above it they come from a matrix product.
 ROUTE_FUSED_MAX_TOKENS = 64
+# ... and up to this many router weights: every token's CTA reads the whole matrix, a chain of latencies that a
+# weight-streaming product spread over the GPU does not have (64 outputs at width 2,048, batch 8: the routing kernel 18 us
+# on its own, 7 with the logits from the product; the decode step 0.878 -> 0.849 ms; 16 outputs at width 1,024: no difference)
+ROUTE_FUSED_MAX_WEIGHTS = 65536
 # Which kernel takes the grouped products of steps with many rows per expert in bfloat16: "auto": the TMA + tcgen05
 # kernel where it takes the sizes (expert matrices of at least 256 rows), else the mma.sync kernel; "mma": the
 # mma.sync kernel always (tests run both).
@@ -131,7 +135,8 @@ class RoutedExperts(FeedForward):
         ids = ws.get("moe_ids", (T, top), torch.int32)
         wts = ws.get("moe_wts", (T, top), torch.float32)
         logits = None
-        if x.dtype == torch.float32 or T > ROUTE_FUSED_MAX_TOKENS or H > K.ROUTE_FUSED_MAX_ROW:
+        if (x.dtype == torch.float32 or T > ROUTE_FUSED_MAX_TOKENS or H > K.ROUTE_FUSED_MAX_ROW
+                or self.router.numel() > ROUTE_FUSED_MAX_WEIGHTS):
             # many tokens: the logits as one product (float32 out: bfloat16 operands multiply exactly, sums are float).
             # float32 always takes this way: its product sums k in one fixed order whatever the step holds, so a
             # token's scores do not change by a bit with its neighbours
