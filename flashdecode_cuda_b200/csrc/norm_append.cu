@@ -9,6 +9,8 @@
 //   v_pool [blocks, n_kv, block_size, nv / n_kv]   nv == 0: no values are kept (the keys serve as values)
 //   k_rows [T, nk] (optional)          the normed k once more as plain rows, for a product that follows
 // nq == 0: there is no q (the rows are keys and values only).
+// q_count / k_count: how many of q's and k's columns are real (the rest are zero padding that brings head sizes to
+// multiples of 8): the means of the squares are taken over these counts.  0: all of them.
 //
 // With n_kv = 1 and nv = 0 the "key" is any normed vector per position, e.g. the
 // low-rank latent that a latent-attention mixer makes its keys and values from.
@@ -23,7 +25,8 @@ __global__ void norm_append_kernel(const T* __restrict__ proj, int ld, T* __rest
                                    const int* __restrict__ tok_row, const int* __restrict__ tok_pos,
                                    const int* __restrict__ row_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                    const int* __restrict__ block_table, int max_blocks, int num_blocks, int block_size,
-                                   int nq, int nk, int nv, int n_kv, int write_kv, T* __restrict__ k_rows, int* status) {
+                                   int nq, int nk, int nv, int n_kv, int write_kv, T* __restrict__ k_rows, int q_count, int k_count,
+                                   int* status) {
     __shared__ float red[40];
     const int t = blockIdx.x;
     const int slot = row_slot[tok_row[t]];
@@ -34,8 +37,8 @@ __global__ void norm_append_kernel(const T* __restrict__ proj, int ld, T* __rest
         for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = to_float(row[i]); sq += v * v; }
     if (k_w != nullptr)
         for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = to_float(row[nq + i]); sk += v * v; }
-    const float rq = q_w != nullptr ? rsqrtf(block_sum(sq, red) / (float)nq + eps) : 1.f;
-    const float rk = k_w != nullptr ? rsqrtf(block_sum(sk, red) / (float)nk + eps) : 1.f;
+    const float rq = q_w != nullptr ? rsqrtf(block_sum(sq, red) / (float)q_count + eps) : 1.f;
+    const float rk = k_w != nullptr ? rsqrtf(block_sum(sk, red) / (float)k_count + eps) : 1.f;
     T* qo = q_out + (size_t)t * nq;
     for (int i = threadIdx.x; i < nq; i += blockDim.x) {
         const float v = to_float(row[i]);
@@ -80,7 +83,8 @@ __global__ void norm_append_vec_kernel(const T* __restrict__ proj, int ld, T* __
                                        const int* __restrict__ tok_row, const int* __restrict__ tok_pos,
                                        const int* __restrict__ row_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                        const int* __restrict__ block_table, int max_blocks, int num_blocks, int block_size,
-                                       int nq, int nk, int nv, int n_kv, int write_kv, T* __restrict__ k_rows, int* status) {
+                                       int nq, int nk, int nv, int n_kv, int write_kv, T* __restrict__ k_rows, int q_count, int k_count,
+                                   int* status) {
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float red[40];
     const int t = blockIdx.x;
@@ -109,8 +113,8 @@ __global__ void norm_append_vec_kernel(const T* __restrict__ proj, int ld, T* __
 #pragma unroll
             for (int j = 0; j < VEC; ++j) sk += f[j] * f[j];
         }
-    const float rq = q_w != nullptr ? rsqrtf(block_sum(sq, red) / (float)nq + eps) : 1.f;
-    const float rk = k_w != nullptr ? rsqrtf(block_sum(sk, red) / (float)nk + eps) : 1.f;
+    const float rq = q_w != nullptr ? rsqrtf(block_sum(sq, red) / (float)q_count + eps) : 1.f;
+    const float rk = k_w != nullptr ? rsqrtf(block_sum(sk, red) / (float)k_count + eps) : 1.f;
     // one piece of the row at `at`, scaled by r * w[...] if w is given, as it goes to memory
     auto piece = [&](int at, const float* w, float r) -> uint4 {
         float f[VEC];
@@ -162,9 +166,11 @@ typedef __nv_bfloat16 bf16;
 extern "C" int fd_norm_append(const void* proj, int ld, void* q_out, int dtype, const float* q_w, const float* k_w,
                               float eps, const int* tok_row, const int* tok_pos, const int* row_slot, void* k_pool,
                               void* v_pool, const int* block_table, int max_blocks, int num_blocks, int block_size, int T,
-                              int nq, int nk, int nv, int n_kv, int write_kv, void* k_rows, int* status,
-                              cudaStream_t stream) {
+                              int nq, int nk, int nv, int n_kv, int write_kv, void* k_rows, int q_count, int k_count,
+                              int* status, cudaStream_t stream) {
     if (T == 0) return 0;
+    if (q_count <= 0) q_count = nq;
+    if (k_count <= 0) k_count = nk;
     FD_REQUIRE(nq >= 0 && (nq == 0 || q_out != nullptr) && nk > 0 && nv >= 0 && n_kv > 0 && nk % n_kv == 0 && nv % n_kv == 0 && ld >= nq + nk + nv, -2,
                "norm_append: %d + %d + %d columns of %d for %d key heads", nq, nk, nv, ld, n_kv);
     FD_REQUIRE(block_size > 0 && (nv == 0 || v_pool != nullptr), -2, "norm_append: bad cache arguments");
@@ -178,19 +184,19 @@ extern "C" int fd_norm_append(const void* proj, int ld, void* q_out, int dtype, 
             return launch("norm_append", norm_append_vec_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
                           (const float*)proj, ld, (float*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (float*)k_pool,
                           (float*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv,
-                          (float*)k_rows, status);
+                          (float*)k_rows, q_count, k_count, status);
         return launch("norm_append", norm_append_vec_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
                       (const bf16*)proj, ld, (bf16*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (bf16*)k_pool,
                       (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv,
-                      (bf16*)k_rows, status);
+                      (bf16*)k_rows, q_count, k_count, status);
     }
     if (dtype == 0)
         return launch("norm_append", norm_append_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
                       (const float*)proj, ld, (float*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (float*)k_pool,
                       (float*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv,
-                      (float*)k_rows, status);
+                      (float*)k_rows, q_count, k_count, status);
     return launch("norm_append", norm_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1),
                   (const bf16*)proj, ld, (bf16*)q_out, q_w, k_w, eps, tok_row, tok_pos, row_slot, (bf16*)k_pool,
                   (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, nq, nk, nv, n_kv, write_kv,
-                  (bf16*)k_rows, status);
+                  (bf16*)k_rows, q_count, k_count, status);
 }

@@ -108,7 +108,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_lanes_norm": [P, I, I, LL, P, P, P, P, I, P, P, F, P, I, P, I, I, I, P],
         "fd_lanes_fill": [P, P, I, I, I, P],
         "fd_lanes_sum": [P, I, P, P, P, P, P, I, I, I, P],
-        "fd_norm_append": [P, I, P, I, P, P, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P],
+        "fd_norm_append": [P, I, P, I, P, P, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, P, P],
         "fd_head_gemm": [P, P, P, I, I, I, I, I, P],
         "fd_moe_align": [P, I, I, P, P, P, P, I, I, P],
         "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, F, P],
@@ -310,11 +310,14 @@ def lanes_sum(y: Optional[torch.Tensor], gain: Optional[torch.Tensor], mix: Opti
 def norm_append(proj: torch.Tensor, q_out: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
                 k_weight: Optional[torch.Tensor], eps: float, tok_row: torch.Tensor, tok_pos: torch.Tensor,
                 row_slot: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor], block_table: torch.Tensor,
-                n_kv: int, write_kv: bool, status: torch.Tensor, k_rows: Optional[torch.Tensor] = None) -> None:
+                n_kv: int, write_kv: bool, status: torch.Tensor, k_rows: Optional[torch.Tensor] = None,
+                q_count: int = 0, k_count: int = 0) -> None:
     """``proj`` [T, >= nq + nk + nv] = [q | k | v]: q (normed over all its nq columns with ``q_weight``, or as it is) to
     ``q_out`` [T, nq]; k (normed over all its nk columns with ``k_weight``, or as it is) and v to the pools at each
     token's position.  ``v_pool`` None: nothing but the keys is kept.  ``q_out`` None: the rows hold no q.  ``k_rows``
-    [T, nk]: receives the (normed) k once more as plain rows.  Norm weights float32."""
+    [T, nk]: receives the (normed) k once more as plain rows.  ``q_count`` / ``k_count``: how many of q's and k's
+    columns are real where heads are zero-padded to multiples of 8 (the norms' means run over these; 0: all).  Norm
+    weights float32."""
     T, ld = proj.shape
     nq = 0 if q_out is None else q_out.shape[1]
     num_blocks, kvh, block_size, d = k_pool.shape
@@ -327,7 +330,7 @@ def norm_append(proj: torch.Tensor, q_out: Optional[torch.Tensor], q_weight: Opt
     _check(lib().fd_norm_append(_ptr(proj), ld, _ptr(q_out), _dt(proj.dtype), _ptr(q_weight), _ptr(k_weight), float(eps),
                                 _ptr(tok_row), _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool),
                                 _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, nq, nk, nv, n_kv,
-                                int(write_kv), _ptr(k_rows), _ptr(status), _stream()))
+                                int(write_kv), _ptr(k_rows), int(q_count), int(k_count), _ptr(status), _stream()))
 
 
 HEAD_GEMM_LIBRARY_ROWS = 64      # from this many rows on, the per-head products of bfloat16 steps go to the library's batched product

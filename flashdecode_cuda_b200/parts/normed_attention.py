@@ -35,11 +35,27 @@ def decode_splits(ctx, n_q: int, n_kv: int, v_dim: int, dtype: torch.dtype, rt: 
     return n_splits, split_len, scratch
 
 
+def _up8(n: int) -> int:
+    return -(-n // 8) * 8
+
+
 def _head_sizes_ok(prefix: str, **sizes: int) -> None:
+    """The attention kernels take head sizes that are multiples of 8 up to 512; other sizes are padded with zeros to
+    the next multiple when the weights are bound (zero rows of the projections, zero norm weights), which changes no
+    score and no output."""
     for what, n in sizes.items():
-        if n < 8 or n > 512 or n % 8 != 0:
-            raise ValueError(f"{prefix}: {what.replace('_', ' ')} {n} is not taken: the attention kernels take multiples "
-                             f"of 8 from 8 to 512")
+        if n < 1 or _up8(n) > 512:
+            raise ValueError(f"{prefix}: {what.replace('_', ' ')} {n} is not taken: the attention kernels take sizes "
+                             f"from 1 to 512")
+
+
+def _pad_heads(w: torch.Tensor, n_heads: int, size: int, padded: int) -> torch.Tensor:
+    """w [n_heads * size, ...] -> [n_heads * padded, ...]: zero rows after every head's own."""
+    if size == padded:
+        return w
+    out = w.new_zeros((n_heads, padded) + tuple(w.shape[1:]))
+    out[:, :size] = w.view((n_heads, size) + tuple(w.shape[1:]))
+    return out.view((n_heads * padded,) + tuple(w.shape[1:]))
 
 
 @register_part("mixer", "qk_normed_attention")
@@ -69,6 +85,7 @@ class QKNormedAttention(Mixer):
             raise ValueError(f"{prefix}: a window of {window} positions")
         self.prefix, self.hidden_size = prefix, hidden_size
         self.n_q, self.n_kv, self.d, self.dv = n_heads, n_kv_heads, head_dim, v_head_dim
+        self.dp, self.dvp = _up8(head_dim), _up8(v_head_dim)         # head sizes as the kernels see them
         self.scale, self.eps, self.window, self.qk_norm = float(scale), float(eps), window, qk_norm
 
     def _sizes(self):
@@ -84,15 +101,22 @@ class QKNormedAttention(Mixer):
         return specs
 
     def kv_request(self) -> KVRequest:
-        return KVRequest(self.n_kv, self.d, self.window, None, self.dv)
+        return KVRequest(self.n_kv, self.dp, self.window, None, self.dvp)
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         p = self.prefix
-        self.w_in = torch.cat([tensors.pop(f"{p}.{n}") for n, _ in self._sizes()], dim=0).contiguous()
-        self.q_norm = tensors[f"{p}.q.norm"].float().contiguous() if self.qk_norm else None
-        self.k_norm = tensors[f"{p}.k.norm"].float().contiguous() if self.qk_norm else None
-        self.w_o = tensors[f"{p}.o"]
+        heads = {"q": (self.n_q, self.d, self.dp), "k": (self.n_kv, self.d, self.dp), "v": (self.n_kv, self.dv, self.dvp)}
+        self.w_in = torch.cat([_pad_heads(tensors.pop(f"{p}.{n}"), *heads[n]) for n, _ in self._sizes()], dim=0).contiguous()
+        self.q_norm = self.k_norm = None
+        if self.qk_norm:
+            self.q_norm = _pad_heads(tensors[f"{p}.q.norm"].float(), *heads["q"]).contiguous()
+            self.k_norm = _pad_heads(tensors[f"{p}.k.norm"].float(), *heads["k"]).contiguous()
+        w_o = tensors[f"{p}.o"]
+        if self.dvp != self.dv:             # zero columns where the padded value dimensions arrive
+            w_o = _pad_heads(w_o.t().contiguous(), self.n_q, self.dv, self.dvp).t().contiguous()
+            tensors[f"{p}.o"] = w_o
+        self.w_o = w_o
 
     def weight_bytes(self) -> int:
         return self.w_in.numel() * self.w_in.element_size() + self.w_o.numel() * self.w_o.element_size()
@@ -104,13 +128,14 @@ class QKNormedAttention(Mixer):
         T, ws, rt = ctx.T, ctx.ws, self.rt
         proj = ws.get("nat_proj", (T, self.w_in.shape[0]), x.dtype)
         matmul(x, self.w_in, None, proj, status=rt.status)
-        q = ws.get("nat_q", (T, self.n_q * self.d), x.dtype)
+        q = ws.get("nat_q", (T, self.n_q * self.dp), x.dtype)
         K.norm_append(proj, q, self.q_norm, self.k_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool,
-                      lc.v_pool, lc.group.table, self.n_kv, lc.writes, rt.status)
-        attn = ws.get("nat_attn", (T, self.n_q * self.dv), x.dtype)
-        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, self.n_kv, self.dv, x.dtype, rt, self.d)
+                      lc.v_pool, lc.group.table, self.n_kv, lc.writes, rt.status, q_count=self.n_q * self.d,
+                      k_count=self.n_kv * self.d)
+        attn = ws.get("nat_attn", (T, self.n_q * self.dvp), x.dtype)
+        n_splits, split_len, scratch = decode_splits(ctx, self.n_q, self.n_kv, self.dvp, x.dtype, rt, self.dp)
         K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
-                    ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d, self.scale,
+                    ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.dp, self.scale,
                     self.window or 0, n_splits, split_len, scratch, rt.status)
         out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
         return matmul(attn, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)
@@ -141,20 +166,22 @@ class LatentAttention(Mixer):
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int, kv_rank: int,
                  scale: float, eps: float, window: Optional[int] = None):
         _head_sizes_ok(prefix, latent_size=kv_rank)
-        if n_heads < 1 or n_heads > (64 if kv_rank <= 256 else 32) or head_dim < 1 or v_head_dim < 1:
+        if n_heads < 1 or n_heads > (64 if _up8(kv_rank) <= 256 else 32) or head_dim < 1 or v_head_dim < 1:
             raise ValueError(f"{prefix}: {n_heads} heads of {head_dim} / {v_head_dim}: the attention kernel takes up to 64 "
                              f"query heads on the one latent (32 on a latent wider than 256)")
         self.prefix, self.hidden_size = prefix, hidden_size
-        self.n_q, self.d, self.dv, self.r = n_heads, head_dim, v_head_dim, kv_rank
+        self.n_q, self.d, self.dv, self.r_true = n_heads, head_dim, v_head_dim, kv_rank
+        self.r = _up8(kv_rank)                     # the latent as the kernels see it: zero-padded to a multiple of 8
         self.scale, self.eps, self.window = float(scale), float(eps), window
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, H = self.prefix, self.hidden_size
+        r = self.r_true
         return [TensorSpec(f"{p}.q", (self.n_q * self.d, H), init="unit"),
-                TensorSpec(f"{p}.dkv", (self.r, H), init="unit"),
-                TensorSpec(f"{p}.dkv.norm", (self.r,), "vector", init="norm"),
-                TensorSpec(f"{p}.uk", (self.n_q * self.d, self.r), init="unit"),
-                TensorSpec(f"{p}.uv", (self.n_q * self.dv, self.r), init="unit"),
+                TensorSpec(f"{p}.dkv", (r, H), init="unit"),
+                TensorSpec(f"{p}.dkv.norm", (r,), "vector", init="norm"),
+                TensorSpec(f"{p}.uk", (self.n_q * self.d, r), init="unit"),
+                TensorSpec(f"{p}.uv", (self.n_q * self.dv, r), init="unit"),
                 TensorSpec(f"{p}.o", (H, self.n_q * self.dv), init="unit")]
 
     def kv_request(self) -> KVRequest:
@@ -163,10 +190,13 @@ class LatentAttention(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         p = self.prefix
-        self.w_in = torch.cat([tensors.pop(f"{p}.q"), tensors.pop(f"{p}.dkv")], dim=0).contiguous()     # [q | latent]
-        self.c_norm = tensors[f"{p}.dkv.norm"].float().contiguous()
+        pad = lambda w: _pad_heads(w, 1, self.r_true, self.r)            # zero rows up to the padded latent size
+        self.w_in = torch.cat([tensors.pop(f"{p}.q"), pad(tensors.pop(f"{p}.dkv"))], dim=0).contiguous()     # [q | latent]
+        self.c_norm = pad(tensors[f"{p}.dkv.norm"].float()).contiguous()
         # per head: U_h^T [kv_rank, head_dim] takes a query into the latent's basis; V_h [v_head_dim, kv_rank]
         uk, uv = tensors.pop(f"{p}.uk"), tensors.pop(f"{p}.uv")
+        if self.r != self.r_true:
+            uk, uv = pad(uk.t().contiguous()).t().contiguous(), pad(uv.t().contiguous()).t().contiguous()
         self.w_qc = uk.view(self.n_q, self.d, self.r).transpose(1, 2).contiguous()
         self.w_cv = uv.view(self.n_q, self.dv, self.r).contiguous()
         self.w_o = tensors[f"{p}.o"]
@@ -194,7 +224,7 @@ class LatentAttention(Mixer):
             # whole prompts: expand the step's own keys and values and attend over them
             c = ws.get("lat_c", (T, self.r), x.dtype)
             K.norm_append(proj, q, None, self.c_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, None,
-                          lc.group.table, 1, lc.writes, rt.status, k_rows=c)
+                          lc.group.table, 1, lc.writes, rt.status, k_rows=c, k_count=self.r_true)
             kv = ws.get("lat_kv", (T, self.w_kv.shape[0]), x.dtype)
             matmul(c, self.w_kv, None, kv, status=rt.status)
             bs = lc.group.block_size
@@ -214,7 +244,7 @@ class LatentAttention(Mixer):
                         rt.status)
             return matmul(av, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)
         K.norm_append(proj, q, None, self.c_norm, self.eps, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, None,
-                      lc.group.table, 1, lc.writes, rt.status)
+                      lc.group.table, 1, lc.writes, rt.status, k_count=self.r_true)
         qc = ws.get("lat_qc", (T, self.n_q * self.r), x.dtype)
         K.head_gemm(q, self.w_qc, qc)
         ac = ws.get("lat_ac", (T, self.n_q * self.r), x.dtype)

@@ -66,6 +66,11 @@ NIZAZEN: Dict[str, dict] = {
     "S": {"architecture": "Nizazen", "vocab": 120, "width": 64, "norm": {"eps": 1e-5}, "streams": 2, "logit_softcap": 20.0,
           "layers": [_layer(_lat(2, 64, 64, 24, 0.125), _dense(48)),
                      _layer(_lat(3, 128, 128, 192, 0.09, 50), _moe(3, 2, 16, 1.0))]},
+    # head sizes and a latent that are no multiple of 8 (padded with zeros when the weights are bound), odd width
+    "T": {"architecture": "Nizazen", "vocab": 77, "width": 50, "norm": {"eps": 1e-5}, "streams": 2,
+          "layers": [_layer(_att(4, 2, 20, 12, 0.22, 11), _moe(3, 2, 10, 1.5)),
+                     _layer(_lat(3, 10, 6, 27, 0.3), _dense(30)),
+                     _layer(_lat(2, 5, 9, 12, 0.4, 13), None)]},
 }
 
 

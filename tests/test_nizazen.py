@@ -75,7 +75,7 @@ def test_blueprint_parts_lanes_and_cache_groups():
 
 def test_a_head_size_no_kernel_takes_is_refused_when_the_model_is_built():
     raw = copy.deepcopy(NIZAZEN["R"])
-    raw["layers"][1]["mixer"]["kv_rank"] = 20
+    raw["layers"][1]["mixer"]["kv_rank"] = 520
     with pytest.raises(ValueError):
         Model.from_config(fd.load_config(raw), torch.float32, "cpu")
 

@@ -25,7 +25,7 @@ from plain import nizazen_plain as P
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 DEV = "cuda"
-NAMES = ["P", "Q", "R", "S"]
+NAMES = ["P", "Q", "R", "S", "T"]
 DTYPES = ["float32", "bfloat16"]
 TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 KTOL = {"float32": 2e-5, "bfloat16": 2e-2}
@@ -323,7 +323,7 @@ def _vocab(name):
 
 def _lengths(name):
     return {"P": [1, 2, 19, 20, 21, 75, 140], "Q": [3, 64, 65, 260], "R": [1, 9, 10, 17, 18, 129],
-            "S": [1, 2, 50, 51, 130, 200]}[name]
+            "S": [1, 2, 50, 51, 130, 200], "T": [1, 11, 12, 14, 90]}[name]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -364,7 +364,7 @@ def test_prefill_then_token_by_token_across_window_edges(engines, folders, name,
     """A prompt, then so many single tokens that every window of the model passes over decoded tokens only."""
     eng = engines[(name, dtype)]
     cache = eng.model.new_cache(max_tokens=256, block_size=16)
-    n_decode = {"P": 150, "Q": 80, "R": 40, "S": 70}[name]
+    n_decode = {"P": 150, "Q": 80, "R": 40, "S": 70, "T": 40}[name]
     for head in (1, 30):
         (p,) = prompts_for(_vocab(name), [head + n_decode], seed=3 + head)
         want = oracle_logits(folders[(name, dtype)], p)
